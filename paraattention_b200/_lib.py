@@ -1,0 +1,89 @@
+"""ctypes binding of libpa_b200.so (declarations mirror include/pa_b200.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PA_MAX_CHUNKS = 8
+PA_OK, PA_EINVAL, PA_ENOTSUP, PA_ECUDA, PA_ETIMEDOUT = 0, -1, -2, -3, -4
+PA_BF16, PA_F16 = 0, 1
+DEV_STATUS_NAMES = {
+    0: "ok",
+    1: "timeout on an in-kernel pipeline barrier",
+    2: "timeout waiting for a query chunk",
+    3: "timeout waiting for a key/value chunk",
+    4: "timeout waiting for the output-arrival counter",
+}
+
+LIB_PATH = Path(__file__).resolve().parent / "libpa_b200.so"
+
+
+class PaError(RuntimeError):
+    """A libpa_b200 entry point returned a negative status."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"libpa_b200 error {code}: {msg}")
+        self.code = code
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("seq_q", C.c_int32), ("seq_kv", C.c_int32),
+        ("head_dim", C.c_int32), ("dtype", C.c_int32), ("is_causal", C.c_int32), ("scale", C.c_float),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("o_stride", C.c_int64 * 3),
+        ("status", C.c_void_p), ("wait_limit_ns", C.c_uint64),
+    ]
+
+
+class CpAttnArgs(C.Structure):
+    _fields_ = [
+        ("q_stage", C.c_void_p), ("k_stage", C.c_void_p), ("v_stage", C.c_void_p),
+        ("batch", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32),
+        ("n_q_chunks", C.c_int32), ("q_rows", C.c_int32), ("q_first", C.c_int32),
+        ("n_kv_chunks", C.c_int32), ("kv_rows", C.c_int32), ("kv_first", C.c_int32),
+        ("scale", C.c_float),
+        ("out", C.c_void_p * PA_MAX_CHUNKS), ("lse", C.c_void_p * PA_MAX_CHUNKS),
+        ("o_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
+        ("out_head_offset", C.c_int32),
+        ("q_flag", C.c_void_p * PA_MAX_CHUNKS), ("kv_flag", C.c_void_p * PA_MAX_CHUNKS),
+        ("flag_expect", C.c_uint32),
+        ("done_flag", C.c_void_p * PA_MAX_CHUNKS),
+        ("status", C.c_void_p), ("wait_limit_ns", C.c_uint64),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m paraattention_b200.build_ext` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    lib.pa_last_error.restype = C.c_char_p
+    lib.pa_last_error.argtypes = []
+    lib.pa_version.restype = C.c_int
+    lib.pa_attn_fwd.restype = C.c_int
+    lib.pa_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    lib.pa_dbg_attn_fwd.restype = C.c_int
+    lib.pa_dbg_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+    lib.pa_cp_attn_fwd.restype = C.c_int
+    lib.pa_cp_attn_fwd.argtypes = [C.POINTER(CpAttnArgs), C.c_void_p]
+    _lib = lib
+    return lib
+
+
+def check(rc: int) -> None:
+    if rc != PA_OK:
+        raise PaError(rc, load().pa_last_error().decode())

@@ -1,0 +1,458 @@
+// Flash-attention forward for B200 (sm_100a): tcgen05 MMA with TMEM accumulators, TMA loads.
+//
+// One CTA owns two query tiles of 128 rows (same batch/head/chunk) and walks every key/value
+// tile of 128 rows. Warp roles:
+//   warps 0-3  softmax for query tile 0 (one thread per row, TMEM lane = row)
+//   warps 4-7  softmax for query tile 1
+//   warp  8    MMA issuer (one thread): S_t = Q_t K_j^T into TMEM, O_t += P_t V_j from TMEM
+//   warp  9    TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
+// TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512);
+// P_t (bf16/f16, 64 columns) overwrites the front of S_t and is the TMEM A operand of P V.
+// While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs.
+//
+// Key/value rows come as a list of equally sized chunks (one per source rank in context
+// parallel runs, one in total otherwise); running max / sum / O stay on chip across
+// chunks, so no out/LSE merge pass exists. A chunk whose ready counter is given is waited
+// for (bounded) by the producer just before its first tile is loaded.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#include "../../include/pa_b200.h"
+#include "pa_ptx.cuh"
+
+namespace pa {
+
+constexpr int kHeadDim = 128;
+constexpr int kTileM = 128;
+constexpr int kTileN = 128;
+constexpr int kHalfBytes = 128 * 128;       // 128 rows x 64 elements x 2 B (one swizzle atom wide)
+constexpr int kTileBytes = 2 * kHalfBytes;  // 128 x 128 x 2 B
+constexpr int kStages = 2;
+constexpr int kSoftmaxWarps = 8;
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr int kAttnThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kColS0 = 0, kColO0 = 256;
+// log2-domain growth of the running row maximum that is tolerated before O is rescaled
+constexpr float kRescaleThreshold = 8.0f;
+
+struct AttnParams {
+    int batch, heads;
+    int n_q_chunks, q_rows, q_first;
+    int n_kv_chunks, kv_rows, kv_first;
+    float scale, scale_log2;
+    void* out[PA_MAX_CHUNKS];
+    float* lse[PA_MAX_CHUNKS];
+    long long o_sb, o_sh, o_ss;
+    long long l_sb, l_sh;
+    const uint32_t* q_flag[PA_MAX_CHUNKS];
+    const uint32_t* kv_flag[PA_MAX_CHUNKS];
+    uint32_t flag_expect;
+    uint32_t* done_flag[PA_MAX_CHUNKS];
+    int* status;
+    unsigned long long wait_ns;
+    // debug instantiation only
+    float* dbg_s;      // raw S of CTA 0: [tile][kv tile][row][col]
+    int v_lbo, v_sbo;  // B descriptor of V (bytes)
+    int pv_split;      // 1: issue P V as two N=64 MMAs
+};
+
+struct AttnSmemCtl {
+    uint64_t q_full;
+    uint64_t k_full[kStages], k_empty[kStages];
+    uint64_t v_full[kStages], v_empty[kStages];
+    uint64_t s_full[2], p_full[2], o_done[2];
+    uint64_t teardown;
+    uint32_t tmem_base;
+    int abort;
+};
+
+constexpr int kAttnSmemBytes = 1024 /*align slack*/ + 2 * kTileBytes /*Q*/ +
+                               kStages * kTileBytes /*K*/ + kStages * kTileBytes /*V*/ +
+                               256 /*control*/;
+static_assert(sizeof(AttnSmemCtl) <= 256, "control block too large");
+
+template <bool kBF16, bool kDebug>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+    const uint32_t sQ = smem_u32(smem);
+    const uint32_t sK = sQ + 2 * kTileBytes;
+    const uint32_t sV = sK + kStages * kTileBytes;
+    AttnSmemCtl* ctl = reinterpret_cast<AttnSmemCtl*>(smem + 2 * kTileBytes + 2 * kStages * kTileBytes);
+    volatile int* s_abort = &ctl->abort;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // A grid in which some CTA already gave up drains without touching TMEM or TMA.
+    if (threadIdx.x == 0) {
+        int st = 0;
+        if (p.status != nullptr) st = *reinterpret_cast<volatile int*>(p.status);
+        ctl->abort = st;
+    }
+    __syncthreads();
+    if (ctl->abort != 0) return;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&ctl->q_full), 1);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&ctl->k_full[s]), 1);
+            mbar_init(smem_u32(&ctl->k_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->v_full[s]), 1);
+            mbar_init(smem_u32(&ctl->v_empty[s]), 1);
+        }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(smem_u32(&ctl->s_full[t]), 1);
+            mbar_init(smem_u32(&ctl->p_full[t]), 128);
+            mbar_init(smem_u32(&ctl->o_done[t]), 1);
+        }
+        mbar_init(smem_u32(&ctl->teardown), 1);
+        mbar_init_fence();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    if (warp == kTmaWarp && lane == 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctl->tmem_base;
+
+    // ---- which work unit: (batch, head, query chunk, pair of query tiles) -------------------
+    const int pairs_per_chunk = (p.q_rows + 2 * kTileM - 1) / (2 * kTileM);
+    int unit = blockIdx.x;
+    const int pair = unit % pairs_per_chunk;
+    unit /= pairs_per_chunk;
+    const int head = unit % p.heads;
+    unit /= p.heads;
+    const int bidx = unit % p.batch;
+    unit /= p.batch;
+    const int qc = (p.q_first + unit) % p.n_q_chunks;
+    const int row0 = pair * 2 * kTileM;
+
+    const int tiles_per_chunk = (p.kv_rows + kTileN - 1) / kTileN;
+    const int n_tiles = tiles_per_chunk * p.n_kv_chunks;
+    const uint64_t pipe_limit = p.wait_ns + 1000000000ull;
+
+    if (warp == kTmaWarp) {
+        // =============================== TMA producer ======================================
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            if (p.q_flag[qc] != nullptr) {
+                ok = flag_wait_ge(p.q_flag[qc], p.flag_expect, s_abort, p.status, p.wait_ns,
+                                  PA_DEV_TIMEOUT_Q);
+                fence_proxy_async_global();
+            }
+            if (ok) {
+                const uint32_t bq = smem_u32(&ctl->q_full);
+                mbar_expect_tx(bq, 2 * kTileBytes);
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                        tma_load_5d(sQ + t * kTileBytes + h * kHalfBytes, &tm_q, bq, h * 64,
+                                    row0 + t * kTileM, head, bidx, qc);
+            }
+            int j = 0;
+            for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
+                int c = p.kv_first + ci;
+                if (c >= p.n_kv_chunks) c -= p.n_kv_chunks;
+                if (p.kv_flag[c] != nullptr) {
+                    ok = flag_wait_ge(p.kv_flag[c], p.flag_expect, s_abort, p.status, p.wait_ns,
+                                      PA_DEV_TIMEOUT_KV);
+                    fence_proxy_async_global();
+                    if (!ok) break;
+                }
+                for (int t = 0; t < tiles_per_chunk; ++t, ++j) {
+                    const int st = j & 1;
+                    const uint32_t ph = (j >> 1) & 1;
+                    const uint32_t bk = smem_u32(&ctl->k_full[st]);
+                    const uint32_t bv = smem_u32(&ctl->v_full[st]);
+                    if (j >= kStages) {
+                        ok = mbar_wait(smem_u32(&ctl->k_empty[st]), ph ^ 1, s_abort, p.status,
+                                       pipe_limit, PA_DEV_TIMEOUT_PIPE);
+                        if (!ok) break;
+                    }
+                    mbar_expect_tx(bk, kTileBytes);
+                    tma_load_5d(sK + st * kTileBytes, &tm_k, bk, 0, t * kTileN, head, bidx, c);
+                    tma_load_5d(sK + st * kTileBytes + kHalfBytes, &tm_k, bk, 64, t * kTileN, head,
+                                bidx, c);
+                    if (j >= kStages) {
+                        ok = mbar_wait(smem_u32(&ctl->v_empty[st]), ph ^ 1, s_abort, p.status,
+                                       pipe_limit, PA_DEV_TIMEOUT_PIPE);
+                        if (!ok) {
+                            issued = j + 1;  // K of tile j is in flight, V is not
+                            break;
+                        }
+                    }
+                    mbar_expect_tx(bv, kTileBytes);
+                    tma_load_5d(sV + st * kTileBytes, &tm_v, bv, 0, t * kTileN, head, bidx, c);
+                    tma_load_5d(sV + st * kTileBytes + kHalfBytes, &tm_v, bv, 64, t * kTileN, head,
+                                bidx, c);
+                    issued = j + 1;
+                }
+            }
+            if (*s_abort != 0) {
+                // Leave only once the copies already issued have landed (bounded by time).
+                int none = 0;
+                volatile int* no_abort = &none;
+                mbar_wait(smem_u32(&ctl->q_full), 0, no_abort, nullptr, 100000000ull, 0);
+                for (int jj = (issued > 2 ? issued - 2 : 0); jj < issued; ++jj) {
+                    const int st = jj & 1;
+                    const uint32_t ph = (jj >> 1) & 1;
+                    mbar_wait(smem_u32(&ctl->k_full[st]), ph, no_abort, nullptr, 100000000ull, 0);
+                    mbar_wait(smem_u32(&ctl->v_full[st]), ph, no_abort, nullptr, 100000000ull, 0);
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // =============================== MMA issuer ========================================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN);
+            constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kHeadDim);
+            constexpr uint32_t idesc_pv64 = make_idesc_f16(kBF16, true, kTileM, 64);
+            const uint32_t v_lbo = kDebug ? static_cast<uint32_t>(p.v_lbo) : kHalfBytes;
+            const uint32_t v_sbo = kDebug ? static_cast<uint32_t>(p.v_sbo) : 1024u;
+            const bool pv_split = kDebug ? (p.pv_split != 0) : false;
+
+            auto issue_qk = [&](int t, int st) {
+#pragma unroll
+                for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+                    const uint64_t a = smem_desc_sw128(sQ + t * kTileBytes + off, 16, 1024);
+                    const uint64_t b = smem_desc_sw128(sK + st * kTileBytes + off, 16, 1024);
+                    tc_mma_ss(tmem + kColS0 + t * kTileN, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv = [&](int t, int st, bool acc) {
+#pragma unroll
+                for (int ks = 0; ks < kTileN / 16; ++ks) {
+                    const uint32_t vaddr = sV + st * kTileBytes + ks * 16 * 128;
+                    const uint32_t a = tmem + kColS0 + t * kTileN + ks * 8;
+                    const uint32_t accum = (acc || ks > 0) ? 1u : 0u;
+                    if (!pv_split) {
+                        tc_mma_ts(tmem + kColO0 + t * kHeadDim, a,
+                                  smem_desc_sw128(vaddr, v_lbo, v_sbo), idesc_pv, accum);
+                    } else {
+                        tc_mma_ts(tmem + kColO0 + t * kHeadDim, a,
+                                  smem_desc_sw128(vaddr, v_lbo, v_sbo), idesc_pv64, accum);
+                        tc_mma_ts(tmem + kColO0 + t * kHeadDim + 64, a,
+                                  smem_desc_sw128(vaddr + kHalfBytes, v_lbo, v_sbo), idesc_pv64,
+                                  accum);
+                    }
+                }
+            };
+
+            bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, s_abort, p.status, pipe_limit,
+                                PA_DEV_TIMEOUT_PIPE);
+            ok = ok && mbar_wait(smem_u32(&ctl->k_full[0]), 0, s_abort, p.status, pipe_limit,
+                                 PA_DEV_TIMEOUT_PIPE);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0, 0);
+                tc_commit(smem_u32(&ctl->s_full[0]));
+                issue_qk(1, 0);
+                tc_commit(smem_u32(&ctl->s_full[1]));
+                tc_commit(smem_u32(&ctl->k_empty[0]));
+            }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                const int stn = (j + 1) & 1;
+                const uint32_t phn = ((j + 1) >> 1) & 1;
+                const bool more = (j + 1 < n_tiles);
+                ok = mbar_wait(smem_u32(&ctl->v_full[st]), ph, s_abort, p.status, pipe_limit,
+                               PA_DEV_TIMEOUT_PIPE);
+                if (ok && more)
+                    ok = mbar_wait(smem_u32(&ctl->k_full[stn]), phn, s_abort, p.status, pipe_limit,
+                                   PA_DEV_TIMEOUT_PIPE);
+                if (!ok) break;
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    ok = mbar_wait(smem_u32(&ctl->p_full[t]), j & 1, s_abort, p.status, pipe_limit,
+                                   PA_DEV_TIMEOUT_PIPE);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t, st, j > 0);
+                    tc_commit(smem_u32(&ctl->o_done[t]));
+                    if (t == 1) tc_commit(smem_u32(&ctl->v_empty[st]));
+                    if (more) {
+                        issue_qk(t, stn);
+                        tc_commit(smem_u32(&ctl->s_full[t]));
+                        if (t == 1) tc_commit(smem_u32(&ctl->k_empty[stn]));
+                    }
+                }
+            }
+            if (!ok) {
+                // Nothing may still be running on the tensor core when TMEM is released.
+                int none = 0;
+                volatile int* no_abort = &none;
+                tc_commit(smem_u32(&ctl->teardown));
+                mbar_wait(smem_u32(&ctl->teardown), 0, no_abort, nullptr, 100000000ull, 0);
+            }
+        }
+    } else {
+        // =============================== softmax + epilogue ================================
+        const int t = warp >> 2;
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN;
+        const uint32_t tO = tmem + lane_base + kColO0 + t * kHeadDim;
+        const uint32_t bs = smem_u32(&ctl->s_full[t]);
+        const uint32_t bp = smem_u32(&ctl->p_full[t]);
+        const uint32_t bo = smem_u32(&ctl->o_done[t]);
+        const float sl = p.scale_log2;
+
+        float m_ref = -INFINITY;
+        float l_sum = 0.f;
+        bool ok = true;
+        int j = 0;
+        for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
+            for (int tk = 0; tk < tiles_per_chunk; ++tk, ++j) {
+                const int valid = min(kTileN, p.kv_rows - tk * kTileN);
+                ok = mbar_wait(bs, j & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t s[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, s[c]);
+                tc_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld_fence(s[c]);
+                if (kDebug && p.dbg_s != nullptr && blockIdx.x == 0) {
+                    float* d = p.dbg_s + ((static_cast<size_t>(t) * n_tiles + j) * 128 + row_in_tile) * 128;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) d[c * 32 + i] = __uint_as_float(s[c][i]);
+                }
+                if (valid < kTileN) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
+                }
+                float mx[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    mx[c] = __uint_as_float(s[c][0]);
+#pragma unroll
+                    for (int i = 1; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(s[c][i]));
+                }
+                const float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_ref);
+                const bool grow = (m_new - m_ref) * sl > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = ex2_approx((m_ref - m_new) * sl);
+                    l_sum *= alpha;
+                    m_ref = m_new;
+                    if (j > 0) {
+                        ok = mbar_wait(bo, (j - 1) & 1, s_abort, p.status, pipe_limit,
+                                       PA_DEV_TIMEOUT_PIPE);
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(tO + c * 32, o);
+                            tc_wait_ld();
+                            tmem_ld_fence(o);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(tO + c * 32, o);
+                        }
+                    }
+                }
+                const float neg = -m_ref * sl;
+                float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int c = half * 2 + cc;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c][i]), sl, neg));
+                            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c][i + 1]), sl, neg));
+                            ls[c] += p0 + p1;
+                            pk[cc * 16 + (i >> 1)] = kBF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+                        }
+                    }
+                    tmem_st32(tS + half * 32, pk);
+                }
+                l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                tc_wait_st();
+                tc_fence_before();
+                mbar_arrive(bp);
+            }
+        }
+        if (ok) ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE);
+        if (ok) {
+            tc_fence_after();
+            const int row = row0 + t * kTileM + row_in_tile;
+            const bool in_range = row < p.q_rows;
+            const float inv = 1.0f / l_sum;
+            uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
+                             (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
+                              static_cast<long long>(row) * p.o_ss);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tO + c * 32, o);
+                tc_wait_ld();
+                tmem_ld_fence(o);
+                if (in_range) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 w;
+                        uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
+                            const float b = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                            wp[i] = kBF16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+                        }
+                        *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = w;
+                    }
+                }
+            }
+            if (in_range && p.lse[qc] != nullptr) {
+                p.lse[qc][static_cast<long long>(bidx) * p.l_sb + static_cast<long long>(head) * p.l_sh + row] =
+                    m_ref * p.scale + __logf(l_sum);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (p.done_flag[qc] != nullptr && *s_abort == 0) {
+        // every output store of this CTA is ordered before the counter update
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            red_release_sys_add(p.done_flag[qc], 1u);
+        }
+    }
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+}  // namespace pa

@@ -1,0 +1,243 @@
+// C ABI of libpa_b200: argument validation, tensor-map encoding and kernel launches.
+// No entry point here allocates device memory or synchronises the device.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/pa_b200.h"
+#include "attn_fwd_sm100.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    });
+    return fn;
+}
+
+// 5-D map over [chunk][batch][head][row][128] with element strides (head_dim stride 1); the box is
+// 64 elements x 128 rows with the 128-byte swizzle the MMA descriptors expect.
+int make_map(CUtensorMap* map, const void* base, int dtype, int rows, int heads, int batch, int chunks,
+             int64_t s_row, int64_t s_head, int64_t s_batch, int64_t s_chunk, const char* what) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (enc == nullptr) return fail(PA_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+        return fail(PA_EINVAL, "%s: base pointer must be 16-byte aligned", what);
+    cuuint64_t dims[5] = {128, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads),
+                          static_cast<cuuint64_t>(batch), static_cast<cuuint64_t>(chunks)};
+    int64_t es[4] = {s_row, s_head, s_batch, s_chunk};
+    cuuint64_t strides[4];
+    for (int i = 0; i < 4; ++i) {
+        int64_t s = es[i];
+        if (dims[i + 1] == 1 && (s <= 0 || (s * 2) % 16 != 0)) s = 128;  // never dereferenced
+        if (s <= 0) return fail(PA_EINVAL, "%s: stride %d must be positive", what, i);
+        if ((s * 2) % 16 != 0) return fail(PA_EINVAL, "%s: byte stride %d must be a multiple of 16", what, i);
+        if (static_cast<uint64_t>(s) * 2 >= (1ull << 40)) return fail(PA_EINVAL, "%s: stride %d too large", what, i);
+        strides[i] = static_cast<cuuint64_t>(s) * 2;
+    }
+    cuuint32_t box[5] = {64, 128, 1, 1, 1};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUtensorMapDataType dt = dtype == PA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = enc(map, dt, 5, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(PA_ECUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, int(r));
+    return PA_OK;
+}
+
+template <bool kBF16, bool kDebug>
+int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const pa::AttnParams& p,
+                int grid, cudaStream_t stream) {
+    auto kern = pa::attn_fwd_kernel<kBF16, kDebug>;
+    static bool configured = false;  // per instantiation
+    static std::mutex mu;
+    {
+        std::lock_guard<std::mutex> g(mu);
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pa::kAttnSmemBytes);
+            if (e != cudaSuccess) return fail(PA_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            configured = true;
+        }
+    }
+    kern<<<grid, pa::kAttnThreads, pa::kAttnSmemBytes, stream>>>(mq, mk, mv, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "attention launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int check_common(int head_dim, int dtype, float scale, int is_causal) {
+    if (head_dim != 128) return fail(PA_ENOTSUP, "head_dim %d: only 128 is built", head_dim);
+    if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "dtype %d: expected PA_BF16 or PA_F16", dtype);
+    if (!(scale > 0.f) || !std::isfinite(scale)) return fail(PA_EINVAL, "scale must be positive and finite");
+    if (is_causal) return fail(PA_ENOTSUP, "causal masking is not built");
+    return PA_OK;
+}
+
+int out_checks(const void* out, const int64_t* o_stride) {
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return fail(PA_EINVAL, "out: base pointer must be 16-byte aligned");
+    for (int i = 0; i < 3; ++i)
+        if ((o_stride[i] * 2) % 16 != 0) return fail(PA_EINVAL, "out: byte stride %d must be a multiple of 16", i);
+    return PA_OK;
+}
+
+int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, int v_sbo, int pv_split, bool debug) {
+    if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
+    if (!a->q || !a->k || !a->v || !a->out) return fail(PA_EINVAL, "q, k, v and out must be non-NULL");
+    if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0)
+        return fail(PA_EINVAL, "batch, heads, seq_q and seq_kv must be positive");
+    int rc = check_common(a->head_dim, a->dtype, a->scale, a->is_causal);
+    if (rc != PA_OK) return rc;
+    rc = out_checks(a->out, a->o_stride);
+    if (rc != PA_OK) return rc;
+
+    CUtensorMap mq, mk, mv;
+    rc = make_map(&mq, a->q, a->dtype, a->seq_q, a->heads, a->batch, 1, a->q_stride[2], a->q_stride[1], a->q_stride[0], 0, "q");
+    if (rc != PA_OK) return rc;
+    rc = make_map(&mk, a->k, a->dtype, a->seq_kv, a->heads, a->batch, 1, a->k_stride[2], a->k_stride[1], a->k_stride[0], 0, "k");
+    if (rc != PA_OK) return rc;
+    rc = make_map(&mv, a->v, a->dtype, a->seq_kv, a->heads, a->batch, 1, a->v_stride[2], a->v_stride[1], a->v_stride[0], 0, "v");
+    if (rc != PA_OK) return rc;
+
+    pa::AttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.batch = a->batch;
+    p.heads = a->heads;
+    p.n_q_chunks = 1;
+    p.q_rows = a->seq_q;
+    p.n_kv_chunks = 1;
+    p.kv_rows = a->seq_kv;
+    p.scale = a->scale;
+    p.scale_log2 = a->scale * 1.4426950408889634f;
+    p.out[0] = a->out;
+    p.lse[0] = a->lse;
+    p.o_sb = a->o_stride[0];
+    p.o_sh = a->o_stride[1];
+    p.o_ss = a->o_stride[2];
+    p.l_sb = static_cast<long long>(a->heads) * a->seq_q;
+    p.l_sh = a->seq_q;
+    p.status = a->status;
+    p.wait_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
+    p.dbg_s = dbg_s;
+    p.v_lbo = v_lbo;
+    p.v_sbo = v_sbo;
+    p.pv_split = pv_split;
+
+    const long long pairs = (a->seq_q + 255) / 256;
+    const long long grid = pairs * a->heads * a->batch;
+    if (grid > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (debug) {
+        return a->dtype == PA_BF16 ? launch_attn<true, true>(mq, mk, mv, p, int(grid), s)
+                                   : launch_attn<false, true>(mq, mk, mv, p, int(grid), s);
+    }
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, int(grid), s)
+                               : launch_attn<false, false>(mq, mk, mv, p, int(grid), s);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* pa_last_error(void) { return g_err; }
+int pa_version(void) { return 1; }
+
+int pa_attn_fwd(const pa_attn_args* args, void* stream) {
+    return attn_fwd_impl(args, stream, nullptr, 0, 0, 0, false);
+}
+
+int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo, int pv_split, void* stream) {
+    return attn_fwd_impl(args, stream, dbg_s, v_lbo, v_sbo, pv_split, true);
+}
+
+int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
+    if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
+    if (!a->q_stage || !a->k_stage || !a->v_stage) return fail(PA_EINVAL, "staging pointers must be non-NULL");
+    if (a->batch <= 0 || a->heads <= 0 || a->q_rows <= 0 || a->kv_rows <= 0)
+        return fail(PA_EINVAL, "batch, heads, q_rows and kv_rows must be positive");
+    if (a->n_q_chunks < 1 || a->n_q_chunks > PA_MAX_CHUNKS || a->n_kv_chunks < 1 || a->n_kv_chunks > PA_MAX_CHUNKS)
+        return fail(PA_EINVAL, "chunk counts must be in [1, %d]", PA_MAX_CHUNKS);
+    if (a->q_first < 0 || a->q_first >= a->n_q_chunks || a->kv_first < 0 || a->kv_first >= a->n_kv_chunks)
+        return fail(PA_EINVAL, "q_first / kv_first out of range");
+    int rc = check_common(a->head_dim, a->dtype, a->scale, 0);
+    if (rc != PA_OK) return rc;
+    for (int c = 0; c < a->n_q_chunks; ++c) {
+        if (a->out[c] == nullptr) return fail(PA_EINVAL, "out[%d] is NULL", c);
+        rc = out_checks(a->out[c], a->o_stride);
+        if (rc != PA_OK) return rc;
+    }
+    CUtensorMap mq, mk, mv;
+    const int64_t qs_h = int64_t(a->q_rows) * 128, qs_b = qs_h * a->heads, qs_c = qs_b * a->batch;
+    const int64_t ks_h = int64_t(a->kv_rows) * 128, ks_b = ks_h * a->heads, ks_c = ks_b * a->batch;
+    rc = make_map(&mq, a->q_stage, a->dtype, a->q_rows, a->heads, a->batch, a->n_q_chunks, 128, qs_h, qs_b, qs_c, "q_stage");
+    if (rc != PA_OK) return rc;
+    rc = make_map(&mk, a->k_stage, a->dtype, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, 128, ks_h, ks_b, ks_c, "k_stage");
+    if (rc != PA_OK) return rc;
+    rc = make_map(&mv, a->v_stage, a->dtype, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, 128, ks_h, ks_b, ks_c, "v_stage");
+    if (rc != PA_OK) return rc;
+
+    pa::AttnParams p;
+    memset(&p, 0, sizeof(p));
+    p.batch = a->batch;
+    p.heads = a->heads;
+    p.n_q_chunks = a->n_q_chunks;
+    p.q_rows = a->q_rows;
+    p.q_first = a->q_first;
+    p.n_kv_chunks = a->n_kv_chunks;
+    p.kv_rows = a->kv_rows;
+    p.kv_first = a->kv_first;
+    p.scale = a->scale;
+    p.scale_log2 = a->scale * 1.4426950408889634f;
+    for (int c = 0; c < PA_MAX_CHUNKS; ++c) {
+        // fold the head offset into the base pointers
+        p.out[c] = a->out[c] ? static_cast<void*>(static_cast<uint16_t*>(a->out[c]) + int64_t(a->out_head_offset) * a->o_stride[1]) : nullptr;
+        p.lse[c] = a->lse[c] ? a->lse[c] + int64_t(a->out_head_offset) * a->lse_stride[1] : nullptr;
+        p.q_flag[c] = a->q_flag[c];
+        p.kv_flag[c] = a->kv_flag[c];
+        p.done_flag[c] = a->done_flag[c];
+    }
+    p.o_sb = a->o_stride[0];
+    p.o_sh = a->o_stride[1];
+    p.o_ss = a->o_stride[2];
+    p.l_sb = a->lse_stride[0];
+    p.l_sh = a->lse_stride[1];
+    p.flag_expect = a->flag_expect;
+    p.status = a->status;
+    p.wait_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
+
+    const long long pairs = (a->q_rows + 255) / 256;
+    const long long grid = pairs * a->heads * a->batch * a->n_q_chunks;
+    if (grid > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, int(grid), s)
+                               : launch_attn<false, false>(mq, mk, mv, p, int(grid), s);
+}
+
+}  // extern "C"
