@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the context-parallel attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--heads H] [--seq S] [--mesh UxR]
+
+One "step" is one non-causal bf16 attention over the whole sequence (B=1, D=128) of the
+standalone op sweep: H=24, S=32760 by default (the Wan-2.1-sized row of the sweep; the
+largest row that is a single launch of a few ms on one GPU). With N > 1 (torchrun, one rank
+per GPU) the sequence is sharded over a ulysses x ring mesh and every step is one call of
+``ulysses_attn_func`` / ``ring_attn_func`` / ``UnifiedAttnMode``; total work is fixed, so
+scaling is "strong". Prints ONE JSON line (rank 0).
+
+``--impl reference`` times the CPU restatement of the reference path (oracle/) on the host
+cores on a bounded sample of the same workload; under torchrun only rank 0 works.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "cp_attention_tflops"
+UNIT = "TFLOP/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--heads", type=int, default=24)
+    ap.add_argument("--seq", type=int, default=32760)
+    ap.add_argument("--mesh", default=None, help="UxR, default Nx1 (all Ulysses)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(H, S):
+    return f"attention-op sweep row: bf16 non-causal B=1 H={H} S={S} D=128"
+
+
+def attention_flops(H, S, B=1, D=128):
+    return 4.0 * B * H * S * S * D
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"bf16_tflops": float(d["bf16_tflops"]), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def make_inputs(H, S, seed=0):
+    """Sweep inputs: N(0,1)*0.5, q and k RMS-normalised over D per (head, token), bf16; a
+    per-tensor generator seeded seed + tensor id. Built on the host."""
+    import torch
+
+    outs = []
+    for i in range(3):
+        g = torch.Generator().manual_seed(seed + i)
+        x = torch.randn(1, H, S, 128, generator=g) * 0.5
+        if i < 2:
+            x = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
+        outs.append(x.to(torch.bfloat16))
+    return outs
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the oracle on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_sample(H, S, budget_s=12.0):
+    """Time oracle attention for a slab of query rows of one head against all S keys; grow
+    the slab until about budget_s seconds of CPU work were spent. Returns (TFLOP/s, text)."""
+    import numpy as np
+
+    from oracle import cp_attention_oracle as O
+
+    rng = np.random.default_rng(0)
+    k = rng.standard_normal((1, 1, S, 128)).astype(np.float32) * 0.5
+    v = rng.standard_normal((1, 1, S, 128)).astype(np.float32) * 0.5
+    rows, spent, flops = 512, 0.0, 0.0
+    while spent < budget_s:
+        q = rng.standard_normal((1, 1, rows, 128)).astype(np.float32) * 0.5
+        t0 = time.perf_counter()
+        O.sdpa_with_lse(q, k, v)
+        dt = time.perf_counter() - t0
+        spent += dt
+        flops += 4.0 * rows * S * 128
+        if dt < 2.0 and rows < 8192:
+            rows *= 2
+    return flops / spent / 1e12, f"{int(flops / (4.0 * S * 128))} query rows of one head x all {S} keys, fp32 numpy oracle, {spent:.1f} s"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    H, S = args.heads, args.seq
+    cores = os.cpu_count() or 1
+    vals, sample = [], ""
+    for _ in range(args.warmup):
+        cpu_sample(H, S, budget_s=1.0)
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        v, sample = cpu_sample(H, S, budget_s=max(2.0, 60.0 / max(args.steps, 1)))
+        vals.append(v)
+    wall = time.perf_counter() - t_all
+    value = statistics.mean(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(H, S), "note": "CPU restatement of the reference path (oracle/), host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        # the busiest half of the samples stands for "under load"
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import paraattention_b200 as pa
+    from paraattention_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    H, S = args.heads, args.seq
+    if args.mesh:
+        U, R = (int(x) for x in args.mesh.lower().split("x"))
+    else:
+        U, R = world, 1
+    assert U * R == world and H % U == 0
+    S_pad = (S + world - 1) // world * world  # pad to divisibility by the world size
+    mesh = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        mesh = dist.init_device_mesh("cuda", (R, U), mesh_dim_names=("ring", "ulysses"))
+
+    q_h, k_h, v_h = make_inputs(H, S_pad)
+    if world > 1:
+        q_h, k_h, v_h = (x.chunk(world, dim=-2)[rank].contiguous() for x in (q_h, k_h, v_h))
+    q_h, k_h, v_h = q_h.pin_memory(), k_h.pin_memory(), v_h.pin_memory()
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
+
+    if world == 1:
+        def step(qq, kk, vv):
+            return ops.attention_forward(qq, kk, vv)
+        launches_per_step = 1
+    else:
+        mode = pa.UnifiedAttnMode(mesh)
+
+        def step(qq, kk, vv):
+            with mode:
+                return torch.nn.functional.scaled_dot_product_attention(qq, kk, vv)
+        launches_per_step = 2 + (1 if U > 1 else 0)  # push + attention (+ output-arrival wait)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def timed(fn, n_warm, n_steps):
+        for _ in range(n_warm):
+            fn()
+        sync_all()
+        evs = []
+        for _ in range(n_steps):
+            flush.fill_(1)  # evict q/k/v and staging from L2 between timed iterations
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        sync_all()
+        total_ms = sum(a.elapsed_time(b) for a, b in evs)
+        t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed(lambda: step(q, k, v), max(args.warmup, 3), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    pa.check_device_status()
+
+    flops = attention_flops(H, S_pad)
+    ms_per_step = total_ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12
+
+    # end to end through the public API with host buffers: H2D of q, k, v and D2H of the result
+    e2e = None
+    if not args.no_e2e:
+        out_h = torch.empty((1, q_h.shape[2], H, 128), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            qq, kk, vv = q_h.to(dev, non_blocking=True), k_h.to(dev, non_blocking=True), v_h.to(dev, non_blocking=True)
+            o = step(qq, kk, vv)
+            out_h.copy_(o.transpose(1, 2), non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 10))
+        e2e_ms = timed(e2e_step, 2, n_e2e) / n_e2e
+        e2e = {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": int(3 * q_h.numel() * 2), "d2h_bytes_per_step": int(out_h.numel() * 2)}
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    per_gpu_tflops = value / world
+    if world == 1:
+        roofline = {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": per_gpu_tflops / peaks["bf16_tflops"], "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((H, S)),
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "kernel": "attn_fwd_kernel",
+                    "flops_per_launch": flops}
+    else:
+        # slower of tensor time and NVLink time (770 GB/s measured per direction per GPU)
+        hl = H // U
+        s_loc = S_pad // world
+        sent = (world - 1) * 2 * hl * s_loc * 128 * 2 + (U - 1) * 2 * hl * s_loc * 128 * 2  # K,V to all; Q out + O back
+        t_tc = flops / world / (peaks["bf16_tflops"] * 1e12)
+        t_nv = sent / 770e9
+        roof = max(t_tc, t_nv)
+        roofline = {"bound": "tensor" if t_tc >= t_nv else "nvlink", "achieved": per_gpu_tflops,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": roof / (ms_per_step * 1e-3),
+                    "traffic": None, "peak_source": f"{peaks['source']} cuBLAS bf16 burst; NVLink 770 GB/s measured",
+                    "exchanged_bytes_per_gpu": int(sent), "t_tensor_ms": t_tc * 1e3, "t_nvlink_ms": t_nv * 1e3}
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        cv, sample = cpu_sample(H, S, budget_s=12.0)
+        cpu_baseline = {"value": cv, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload_name(H, S), "mesh": f"{U}x{R} (ulysses x ring)", "per_gpu_tflops": per_gpu_tflops,
+                   "l2": "256 MB flush between timed iterations", "timing": "CUDA events per step, max over ranks"},
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": launches_per_step * args.steps,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from the ncu
+# captures summarised under profiles/ (scaled from the captured case by heads where noted there)
+TRAFFIC_BYTES_PER_LAUNCH = {}
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

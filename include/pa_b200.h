@@ -115,6 +115,81 @@ typedef struct pa_cp_attn_args {
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);
 
+/* Test hook: pa_attn_fwd that also dumps the raw q k^T tiles of the first CTA to dbg_s
+ * ([2][kv_tiles][128][128] floats, may be NULL) and lets the caller choose the shared-memory
+ * descriptor strides of V (v_lbo, v_sbo; bytes) and whether P V is issued as two N=64 MMAs.
+ * No counterpart in the reference. */
+int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo, int pv_split, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Exchange. Replaces the NCCL all_to_all_single calls of _sdpa_input_all_to_all /
+ * _sdpa_output_all_to_all (src/para_attn/para_attn_interface.py:52-87, through
+ * src/para_attn/primitives.py:72-78) and the K/V rotation of torch:_AllToAllRotater
+ * (torch:247-263): each job copies rows [batch, head0..head0+heads, rows, 128] of a local
+ * tensor to dst (normally a peer GPU's mapped staging buffer) with the given element
+ * strides; when all jobs of a destination are stored, flag[dest] on that destination is
+ * increased by ctas_per_dest in total (each CTA adds 1 with a system-scope release).
+ * ---------------------------------------------------------------------------------------- */
+#define PA_MAX_PUSH_JOBS 24
+
+typedef struct pa_push_job {
+    const void* src;
+    void* dst;
+    int64_t src_stride[3];   /* element strides (batch, head, row); 128 contiguous 16-bit elements per row */
+    int64_t dst_stride[3];
+    int32_t head0, heads, batch, rows;
+    int32_t dest;            /* index into pa_cp_push_args.flag */
+    int32_t pad_;
+} pa_push_job;
+
+typedef struct pa_cp_push_args {
+    pa_push_job jobs[PA_MAX_PUSH_JOBS];
+    int32_t n_jobs;
+    int32_t n_dest;
+    uint32_t* flag[PA_MAX_CHUNKS];
+    int32_t ctas_per_dest;
+    int32_t pad_;
+} pa_cp_push_args;
+
+int pa_cp_push(const pa_cp_push_args* args, void* stream);
+
+/* Stream-ordered bounded wait until every flag[i] >= expect (i < n). On timeout the device
+ * status word receives `code` (a pa_device_status value). Stands where the reference calls
+ * .wait() on a functional collective (src/para_attn/primitives.py:36-43). */
+int pa_flag_wait(const uint32_t* const* flag, int32_t n, uint32_t expect, int32_t* status, uint64_t wait_limit_ns,
+                 int32_t code, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Merge of two partial attention results, torch:_SDPAMerger._merge_one (torch:182-183):
+ * acc_out (fp32 [rows, d]) and acc_lse (fp32 [rows]) are updated in place from a block's
+ * out (blk_dtype: PA_BF16, PA_F16 or 2 = fp32) and lse (fp32).
+ * ---------------------------------------------------------------------------------------- */
+int pa_merge_out_lse(float* acc_out, float* acc_lse, const void* blk_out, const float* blk_lse, int64_t rows,
+                     int32_t d, int32_t blk_dtype, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * First Block Cache. pa_fbc_residual_diff fuses the residual formation of
+ * CachedTransformerBlocks.forward (src/para_attn/first_block_cache/utils.py:359) with the two
+ * reductions of are_two_tensors_similar (utils.py:228-229) and the store of
+ * set_first_hidden_states_residual (utils.py:289-295):
+ *   cur = round(h1 - h0); result[0] = sum |round(prev - cur)|; result[1] = sum |prev|;
+ *   result[2], result[3] = the two means rounded to dtype; result[4] = round(result[2]/result[3]).
+ * h1, h0: [rows, cols] contiguous. With downsample > 1 only every downsample-th column takes
+ * part and prev / new_resid are compact [rows, ceil(cols/downsample)]. prev and new_resid may
+ * be NULL (no comparison / no store). result: 5 floats. scratch: pa_fbc_scratch_bytes() bytes
+ * whose last 4 bytes (the ticket) must be zero before the first call; the kernel leaves them
+ * zero. Calls sharing a scratch buffer must not overlap on the GPU.
+ * ---------------------------------------------------------------------------------------- */
+int64_t pa_fbc_scratch_bytes(void);
+int pa_fbc_residual_diff(const void* h1, const void* h0, const void* prev, void* new_resid, int64_t rows,
+                         int32_t cols, int32_t downsample, int32_t dtype, float* result, void* scratch,
+                         void* stream);
+
+/* out = round(a + b) (sub = 0) or round(a - b) (sub = 1), elementwise over numel 16-bit
+ * elements (numel % 8 == 0, 16-byte aligned pointers): apply_prev_hidden_states_residual
+ * (utils.py:237-259) and the residual formation at utils.py:443-444. */
+int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t sub, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -234,7 +234,7 @@ def fbc_decision(sum_diff: Sequence[float], sum_prev: Sequence[float], numel: in
         mean_diff, mean_prev = md[0], mp[0]
     with np.errstate(divide="ignore", invalid="ignore"):
         ratio = bf16_round(np.float32(mean_diff) / np.float32(mean_prev))
-    return bool(float(ratio) < threshold)
+    return bool(float(np.asarray(ratio).reshape(-1)[0]) < threshold)
 
 
 class FbcStateOracle:

@@ -10,6 +10,7 @@ from pathlib import Path
 PA_MAX_CHUNKS = 8
 PA_OK, PA_EINVAL, PA_ENOTSUP, PA_ECUDA, PA_ETIMEDOUT = 0, -1, -2, -3, -4
 PA_BF16, PA_F16 = 0, 1
+PA_DEV_TIMEOUT_PIPE, PA_DEV_TIMEOUT_Q, PA_DEV_TIMEOUT_KV, PA_DEV_TIMEOUT_OUT = 1, 2, 3, 4
 DEV_STATUS_NAMES = {
     0: "ok",
     1: "timeout on an in-kernel pipeline barrier",
@@ -57,6 +58,27 @@ class CpAttnArgs(C.Structure):
     ]
 
 
+PA_MAX_PUSH_JOBS = 24
+
+
+class PushJob(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p), ("dst", C.c_void_p),
+        ("src_stride", C.c_int64 * 3), ("dst_stride", C.c_int64 * 3),
+        ("head0", C.c_int32), ("heads", C.c_int32), ("batch", C.c_int32), ("rows", C.c_int32),
+        ("dest", C.c_int32), ("pad_", C.c_int32),
+    ]
+
+
+class CpPushArgs(C.Structure):
+    _fields_ = [
+        ("jobs", PushJob * PA_MAX_PUSH_JOBS),
+        ("n_jobs", C.c_int32), ("n_dest", C.c_int32),
+        ("flag", C.c_void_p * PA_MAX_CHUNKS),
+        ("ctas_per_dest", C.c_int32), ("pad_", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -80,6 +102,21 @@ def load() -> C.CDLL:
     lib.pa_dbg_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pa_cp_attn_fwd.restype = C.c_int
     lib.pa_cp_attn_fwd.argtypes = [C.POINTER(CpAttnArgs), C.c_void_p]
+    lib.pa_cp_push.restype = C.c_int
+    lib.pa_cp_push.argtypes = [C.POINTER(CpPushArgs), C.c_void_p]
+    lib.pa_flag_wait.restype = C.c_int
+    lib.pa_flag_wait.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_int32,
+                                 C.c_void_p]
+    lib.pa_merge_out_lse.restype = C.c_int
+    lib.pa_merge_out_lse.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                     C.c_void_p]
+    lib.pa_fbc_scratch_bytes.restype = C.c_int64
+    lib.pa_fbc_scratch_bytes.argtypes = []
+    lib.pa_fbc_residual_diff.restype = C.c_int
+    lib.pa_fbc_residual_diff.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                         C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.pa_fbc_axpy.restype = C.c_int
+    lib.pa_fbc_axpy.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
     _lib = lib
     return lib
 

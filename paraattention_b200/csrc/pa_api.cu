@@ -11,6 +11,9 @@
 
 #include "../../include/pa_b200.h"
 #include "attn_fwd_sm100.cuh"
+#include "cp_exchange_sm100.cuh"
+#include "fbc_sm100.cuh"
+#include "merge_sm100.cuh"
 
 namespace {
 
@@ -77,14 +80,16 @@ template <bool kBF16, bool kDebug>
 int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const pa::AttnParams& p,
                 int grid, cudaStream_t stream) {
     auto kern = pa::attn_fwd_kernel<kBF16, kDebug>;
-    static bool configured = false;  // per instantiation
+    static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
     {
+        int dev = 0;
+        cudaGetDevice(&dev);
         std::lock_guard<std::mutex> g(mu);
-        if (!configured) {
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pa::kAttnSmemBytes);
             if (e != cudaSuccess) return fail(PA_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            configured = true;
+            if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
     kern<<<grid, pa::kAttnThreads, pa::kAttnSmemBytes, stream>>>(mq, mk, mv, p);
@@ -238,6 +243,140 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, int(grid), s)
                                : launch_attn<false, false>(mq, mk, mv, p, int(grid), s);
+}
+
+int pa_cp_push(const pa_cp_push_args* a, void* stream) {
+    if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
+    if (a->n_jobs < 0 || a->n_jobs > PA_MAX_PUSH_JOBS) return fail(PA_EINVAL, "n_jobs must be in [0, %d]", PA_MAX_PUSH_JOBS);
+    if (a->n_dest < 1 || a->n_dest > PA_MAX_CHUNKS) return fail(PA_EINVAL, "n_dest must be in [1, %d]", PA_MAX_CHUNKS);
+    if (a->ctas_per_dest < 1 || a->ctas_per_dest > 1024) return fail(PA_EINVAL, "ctas_per_dest must be in [1, 1024]");
+    pa::PushParams p;
+    memset(&p, 0, sizeof(p));
+    for (int j = 0; j < a->n_jobs; ++j) {
+        const pa_push_job& job = a->jobs[j];
+        if (!job.src || !job.dst) return fail(PA_EINVAL, "job %d: src and dst must be non-NULL", j);
+        if (job.dest < 0 || job.dest >= a->n_dest) return fail(PA_EINVAL, "job %d: dest out of range", j);
+        if (job.batch <= 0 || job.heads <= 0 || job.rows <= 0 || job.head0 < 0)
+            return fail(PA_EINVAL, "job %d: batch, heads, rows must be positive", j);
+        if ((reinterpret_cast<uintptr_t>(job.src) & 15u) || (reinterpret_cast<uintptr_t>(job.dst) & 15u))
+            return fail(PA_EINVAL, "job %d: src and dst must be 16-byte aligned", j);
+        for (int i = 0; i < 3; ++i)
+            if ((job.src_stride[i] * 2) % 16 != 0 || (job.dst_stride[i] * 2) % 16 != 0)
+                return fail(PA_EINVAL, "job %d: byte strides must be multiples of 16", j);
+        p.jobs[j] = job;
+    }
+    p.n_jobs = a->n_jobs;
+    p.n_dest = a->n_dest;
+    for (int d = 0; d < PA_MAX_CHUNKS; ++d) p.flag[d] = a->flag[d];
+    dim3 grid(a->ctas_per_dest, a->n_dest);
+    pa::cp_push_kernel<<<grid, pa::kPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "push launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int pa_flag_wait(const uint32_t* const* flag, int32_t n, uint32_t expect, int32_t* status, uint64_t wait_limit_ns,
+                 int32_t code, void* stream) {
+    if (flag == nullptr || n < 1 || n > PA_MAX_CHUNKS) return fail(PA_EINVAL, "flag list must hold 1..%d pointers", PA_MAX_CHUNKS);
+    pa::FlagWaitParams p;
+    memset(&p, 0, sizeof(p));
+    for (int i = 0; i < n; ++i) p.flag[i] = flag[i];
+    p.n = n;
+    p.expect = expect;
+    p.status = status;
+    p.wait_ns = wait_limit_ns ? wait_limit_ns : 2000000000ull;
+    p.code = code;
+    pa::flag_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "flag wait launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int pa_merge_out_lse(float* acc_out, float* acc_lse, const void* blk_out, const float* blk_lse, int64_t rows,
+                     int32_t d, int32_t blk_dtype, void* stream) {
+    if (!acc_out || !acc_lse || !blk_out || !blk_lse) return fail(PA_EINVAL, "merge: NULL pointer");
+    if (rows <= 0 || d <= 0) return fail(PA_EINVAL, "merge: rows and d must be positive");
+    const int threads = 256;
+    long long blocks = (rows + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (blk_dtype) {
+        case 0: pa::merge_out_lse_kernel<0><<<int(blocks), threads, 0, s>>>(acc_out, acc_lse, blk_out, blk_lse, rows, d); break;
+        case 1: pa::merge_out_lse_kernel<1><<<int(blocks), threads, 0, s>>>(acc_out, acc_lse, blk_out, blk_lse, rows, d); break;
+        case 2: pa::merge_out_lse_kernel<2><<<int(blocks), threads, 0, s>>>(acc_out, acc_lse, blk_out, blk_lse, rows, d); break;
+        default: return fail(PA_EINVAL, "merge: blk_dtype must be 0 (bf16), 1 (f16) or 2 (f32)");
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "merge launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int64_t pa_fbc_scratch_bytes(void) { return int64_t(2 * pa::kFbcMaxBlocks) * 4 + 4; }
+
+int pa_fbc_residual_diff(const void* h1, const void* h0, const void* prev, void* new_resid, int64_t rows,
+                         int32_t cols, int32_t downsample, int32_t dtype, float* result, void* scratch,
+                         void* stream) {
+    if (!h1 || !h0 || !result || !scratch) return fail(PA_EINVAL, "fbc: h1, h0, result and scratch must be non-NULL");
+    if (rows <= 0 || cols <= 0 || downsample < 1) return fail(PA_EINVAL, "fbc: rows, cols must be positive and downsample >= 1");
+    if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "fbc: dtype must be PA_BF16 or PA_F16");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* sc = static_cast<float*>(scratch);
+    const long long numel = static_cast<long long>(rows) * cols;
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (downsample == 1 && numel % 8 == 0 && aligned16(h1) && aligned16(h0) && aligned16(prev) && aligned16(new_resid)) {
+        const long long n8 = numel / 8;
+        long long blocks = (n8 + pa::kFbcThreads - 1) / pa::kFbcThreads;
+        if (blocks > pa::kFbcMaxBlocks) blocks = pa::kFbcMaxBlocks;
+        // the ticket sits right behind the partials of this launch's grid
+        if (dtype == PA_BF16)
+            pa::fbc_residual_diff_kernel<true><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint4*>(h1), static_cast<const uint4*>(h0), static_cast<const uint4*>(prev),
+                static_cast<uint4*>(new_resid), n8, sc + 2 * (pa::kFbcMaxBlocks - blocks), result);
+        else
+            pa::fbc_residual_diff_kernel<false><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint4*>(h1), static_cast<const uint4*>(h0), static_cast<const uint4*>(prev),
+                static_cast<uint4*>(new_resid), n8, sc + 2 * (pa::kFbcMaxBlocks - blocks), result);
+    } else {
+        const int cols_ds = (cols + downsample - 1) / downsample;
+        const long long n = static_cast<long long>(rows) * cols_ds;
+        long long blocks = (n + pa::kFbcThreads - 1) / pa::kFbcThreads;
+        if (blocks > pa::kFbcMaxBlocks) blocks = pa::kFbcMaxBlocks;
+        if (dtype == PA_BF16)
+            pa::fbc_residual_diff_strided_kernel<true><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint16_t*>(h1), static_cast<const uint16_t*>(h0), static_cast<const uint16_t*>(prev),
+                static_cast<uint16_t*>(new_resid), rows, cols, downsample, sc + 2 * (pa::kFbcMaxBlocks - blocks), result);
+        else
+            pa::fbc_residual_diff_strided_kernel<false><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint16_t*>(h1), static_cast<const uint16_t*>(h0), static_cast<const uint16_t*>(prev),
+                static_cast<uint16_t*>(new_resid), rows, cols, downsample, sc + 2 * (pa::kFbcMaxBlocks - blocks), result);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "fbc launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t sub, int32_t dtype, void* stream) {
+    if (!a || !b || !out) return fail(PA_EINVAL, "axpy: NULL pointer");
+    if (numel <= 0 || numel % 8 != 0) return fail(PA_EINVAL, "axpy: numel must be a positive multiple of 8");
+    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15u)
+        return fail(PA_EINVAL, "axpy: pointers must be 16-byte aligned");
+    if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "axpy: dtype must be PA_BF16 or PA_F16");
+    const long long n8 = numel / 8;
+    long long blocks = (n8 + pa::kFbcThreads - 1) / pa::kFbcThreads;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint4 *pa_ = static_cast<const uint4*>(a), *pb_ = static_cast<const uint4*>(b);
+    uint4* po = static_cast<uint4*>(out);
+    if (dtype == PA_BF16) {
+        if (sub) pa::fbc_axpy_kernel<true, true><<<int(blocks), pa::kFbcThreads, 0, s>>>(pa_, pb_, po, n8);
+        else pa::fbc_axpy_kernel<true, false><<<int(blocks), pa::kFbcThreads, 0, s>>>(pa_, pb_, po, n8);
+    } else {
+        if (sub) pa::fbc_axpy_kernel<false, true><<<int(blocks), pa::kFbcThreads, 0, s>>>(pa_, pb_, po, n8);
+        else pa::fbc_axpy_kernel<false, false><<<int(blocks), pa::kFbcThreads, 0, s>>>(pa_, pb_, po, n8);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "axpy launch: %s", cudaGetErrorString(e));
+    return PA_OK;
 }
 
 }  // extern "C"

@@ -1,0 +1,137 @@
+"""Attention custom ops, same names and signatures as the reference's ``para_attn.ops``
+(src/para_attn/ops/__init__.py:160-245), backed by the sm_100a kernels of libpa_b200.
+
+``torch.ops.para_attn.attention_forward_with_lse(q, k, v, attn_mask=None, dropout_p=0.0,
+is_causal=False, *, scale=None) -> (out, lse)`` and ``attention_forward(...) -> out``.
+Where the reference picks one of PyTorch's flash / efficient / cuDNN SDPA backends
+(:112-157), these ops launch one tcgen05 flash-attention kernel. They are CUDA-only: a CPU
+tensor raises, nothing falls back to PyTorch math.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+__all__ = [
+    "attention_forward_with_lse",
+    "attention_forward",
+    "merge_out_lse_",
+    "raw_attention_forward",
+]
+
+_DTYPES = {torch.bfloat16: L.PA_BF16, torch.float16: L.PA_F16}
+
+
+def _check_inputs(query, key, value, attn_mask, dropout_p, is_causal):
+    assert query.device.type == "cuda", "Must be CUDA tensors"  # as src/para_attn/ops/__init__.py:123
+    assert query.ndim == 4 and key.ndim == 4 and value.ndim == 4, "query, key and value must be [B, H, S, D]"
+    if query.dtype not in _DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
+        raise NotImplementedError(f"attention dtype {query.dtype}: only bfloat16 and float16 are built")
+    if attn_mask is not None:
+        raise NotImplementedError("attn_mask is not built into the sm_100a attention kernel")
+    if dropout_p != 0.0:
+        raise NotImplementedError("dropout_p must be 0: the library is forward/inference only")
+    if is_causal:
+        raise NotImplementedError("is_causal is not built into the sm_100a attention kernel")
+    if query.shape[-1] != 128 or key.shape[-1] != 128 or value.shape[-1] != 128:
+        raise NotImplementedError(f"head_dim {query.shape[-1]}: only 128 is built")
+    assert key.shape[:2] == query.shape[:2] and value.shape == key.shape, "mismatched batch/head/key shapes"
+
+
+def _tma_ready(x: torch.Tensor) -> torch.Tensor:
+    """Return x itself if the kernel can address it in place (unit stride on head_dim, 16-byte
+    aligned base and strides, no broadcast dims), else a contiguous copy."""
+    ok = x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+    for i in range(3):
+        s = x.stride(i)
+        ok = ok and (x.shape[i] == 1 or (s > 0 and (s * x.element_size()) % 16 == 0))
+    return x if ok else x.contiguous()
+
+
+def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: bool,
+                          status: Optional[torch.Tensor] = None):
+    """Launch pa_attn_fwd on the current stream. Output memory is [B, S, H, D] viewed as
+    [B, H, S, D], the layout PyTorch's flash backend returns, so that the usual
+    ``transpose(1, 2).flatten(2)`` that follows attention is free."""
+    B, H, Sq, D = query.shape
+    Skv = key.shape[2]
+    q, k, v = _tma_ready(query), _tma_ready(key), _tma_ready(value)
+    out = torch.empty((B, Sq, H, D), dtype=query.dtype, device=query.device).transpose(1, 2)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=query.device) if need_lse else None
+    a = L.AttnArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.lse = lse.data_ptr() if lse is not None else None
+    a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = B, H, Sq, Skv, D
+    a.dtype = _DTYPES[query.dtype]
+    a.is_causal = 0
+    a.scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
+    for i in range(3):
+        a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
+    a.status = status.data_ptr() if status is not None else None
+    a.wait_limit_ns = 0
+    L.check(L.load().pa_attn_fwd(C.byref(a), torch.cuda.current_stream(query.device).cuda_stream))
+    return out, lse
+
+
+@torch.library.custom_op("para_attn::attention_forward_with_lse", mutates_args=(), device_types=("cuda",))
+def attention_forward_with_lse(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attn_mask: Optional[torch.Tensor] = None,
+    dropout_p: float = 0.0,
+    is_causal: bool = False,
+    *,
+    scale: Optional[float] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    _check_inputs(query, key, value, attn_mask, dropout_p, is_causal)
+    out, lse = raw_attention_forward(query, key, value, scale, True)
+    return out, lse
+
+
+@torch.library.register_fake("para_attn::attention_forward_with_lse")
+def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None):
+    B, H, Sq, D = query.shape
+    out = query.new_empty((B, Sq, H, D)).transpose(1, 2)
+    lse = query.new_empty((B, H, Sq), dtype=torch.float32)
+    return out, lse
+
+
+@torch.library.custom_op("para_attn::attention_forward", mutates_args=(), device_types=("cuda",))
+def attention_forward(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attn_mask: Optional[torch.Tensor] = None,
+    dropout_p: float = 0.0,
+    is_causal: bool = False,
+    *,
+    scale: Optional[float] = None,
+) -> torch.Tensor:
+    _check_inputs(query, key, value, attn_mask, dropout_p, is_causal)
+    out, _ = raw_attention_forward(query, key, value, scale, False)
+    return out
+
+
+@torch.library.register_fake("para_attn::attention_forward")
+def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None):
+    B, H, Sq, D = query.shape
+    return query.new_empty((B, Sq, H, D)).transpose(1, 2)
+
+
+def merge_out_lse_(acc_out: torch.Tensor, acc_lse: torch.Tensor, block_out: torch.Tensor,
+                   block_lse: torch.Tensor) -> None:
+    """In-place ``_SDPAMerger._merge_one`` (torch/distributed/tensor/experimental/
+    _context_parallel/_attention.py:182-183): acc_out fp32 [..., S, D], acc_lse fp32 [..., S]."""
+    assert acc_out.dtype == torch.float32 and acc_lse.dtype == torch.float32 and block_lse.dtype == torch.float32
+    assert acc_out.is_contiguous() and acc_lse.is_contiguous() and block_out.is_contiguous() and block_lse.is_contiguous()
+    assert acc_out.shape == block_out.shape and acc_lse.shape == block_lse.shape == acc_out.shape[:-1]
+    code = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[block_out.dtype]
+    L.check(L.load().pa_merge_out_lse(acc_out.data_ptr(), acc_lse.data_ptr(), block_out.data_ptr(), block_lse.data_ptr(),
+                                      acc_lse.numel(), acc_out.shape[-1], code,
+                                      torch.cuda.current_stream(acc_out.device).cuda_stream))

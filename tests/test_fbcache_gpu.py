@@ -1,0 +1,140 @@
+"""First-Block-Cache kernels on the GPU against the oracle and the reference's recorded decisions."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cp_attention_oracle as O
+from helpers import bf16_from_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _abi_residual_diff(h1, h0, prev, downsample=1, store=True):
+    from paraattention_b200 import _lib as L
+
+    lib = L.load()
+    cols = h1.shape[-1]
+    rows = h1.numel() // cols
+    cols_ds = (cols + downsample - 1) // downsample
+    cur = torch.empty(tuple(h1.shape[:-1]) + (cols_ds,), dtype=h1.dtype, device="cuda") if store else None
+    result = torch.full((5,), float("nan"), device="cuda")
+    scratch = torch.zeros(int(lib.pa_fbc_scratch_bytes()), dtype=torch.uint8, device="cuda")
+    rc = lib.pa_fbc_residual_diff(h1.data_ptr(), h0.data_ptr(), prev.data_ptr() if prev is not None else None,
+                                  cur.data_ptr() if cur is not None else None, rows, cols, downsample,
+                                  L.PA_BF16 if h1.dtype == torch.bfloat16 else L.PA_F16, result.data_ptr(),
+                                  scratch.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.pa_last_error()
+    torch.cuda.synchronize()
+    # the ticket word must be back to zero so that the scratch can be reused
+    assert int(scratch[-4:].view(torch.int32).item()) == 0
+    return cur, result.cpu().numpy()
+
+
+@pytest.mark.parametrize("shape,ds", [((1, 32, 128), 1), ((2, 333, 3072), 1), ((1, 4096, 3072), 1), ((1, 77, 3072), 2),
+                                      ((1, 50, 130), 1), ((1, 64, 3072), 4)])
+def test_residual_diff_bit_exact_against_oracle(shape, ds):
+    g = torch.Generator().manual_seed(shape[1])
+    h0 = torch.randn(shape, generator=g).bfloat16()
+    h1 = (h0.float() + 0.3 * torch.randn(shape, generator=g)).bfloat16()
+    cols_ds = (shape[-1] + ds - 1) // ds
+    prev = (0.3 * torch.randn(shape[:-1] + (cols_ds,), generator=g)).bfloat16()
+    cur, res = _abi_residual_diff(h1.cuda(), h0.cuda(), prev.cuda(), downsample=ds)
+    want_cur = O.bf16_round(h1.float().numpy() - h0.float().numpy())[..., ::ds]
+    # residual: bit-exact
+    np.testing.assert_array_equal(cur.float().cpu().numpy(), want_cur)
+    sd, sp = O.fbc_partial_sums(prev.float().numpy(), want_cur)
+    n = want_cur.size
+    # fp32 sums: accumulation order differs, values agree to fp32 accuracy
+    np.testing.assert_allclose(res[0], sd, rtol=2e-6)
+    np.testing.assert_allclose(res[1], sp, rtol=2e-6)
+    # the rounded means / ratio the decision is taken from: exact
+    assert res[2] == O.bf16_round(np.float32(res[0]) / np.float32(n))
+    assert res[3] == O.bf16_round(np.float32(res[1]) / np.float32(n))
+    assert O.fbc_decision([res[0]], [res[1]], n, 0.5) == bool(res[4] < 0.5)
+    assert res[4] == O.bf16_round(np.float32(res[2]) / np.float32(res[3]))
+
+
+def test_residual_diff_without_prev_or_store():
+    h0 = torch.randn(1, 16, 256).bfloat16().cuda()
+    h1 = torch.randn(1, 16, 256).bfloat16().cuda()
+    cur, res = _abi_residual_diff(h1, h0, None)
+    assert res[0] == 0.0 and res[1] == 0.0
+    np.testing.assert_array_equal(cur.float().cpu().numpy(), O.bf16_round(h1.float().cpu().numpy() - h0.float().cpu().numpy()))
+    none, res = _abi_residual_diff(h1, h0, cur, store=False)
+    assert none is None and res[0] == 0.0 and res[1] > 0.0
+
+
+def test_axpy_bit_exact():
+    from paraattention_b200 import _lib as L
+
+    lib = L.load()
+    a = torch.randn(3, 1000, 128).bfloat16().cuda()
+    b = torch.randn(3, 1000, 128).bfloat16().cuda()
+    out = torch.empty_like(a)
+    for sub in (0, 1):
+        rc = lib.pa_fbc_axpy(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), sub, L.PA_BF16,
+                             torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        want = (a - b) if sub else (a + b)
+        assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("case,kw", [
+    ("thr008", dict(residual_diff_threshold=0.08)),
+    ("thr003_warm2", dict(residual_diff_threshold=0.03, warmup_steps=2)),
+    ("thr02_ds2", dict(residual_diff_threshold=0.2, downsample_factor=2)),
+    ("thr0", dict(residual_diff_threshold=0.0)),
+])
+def test_cached_blocks_follow_reference_step_by_step(golden_dir, case, kw):
+    """Same scripted sequence as tests/golden/make_golden.py: the skip/compute decision and the
+    block outputs must equal what the reference's CachedTransformerBlocks produced."""
+    from paraattention_b200.first_block_cache import utils as fbc
+
+    g = np.load(golden_dir / "fbcache_steps.npz")
+    h0s, h1s, enc = bf16_from_bits(g["h0"]), bf16_from_bits(g["h1"]), bf16_from_bits(g["enc"])
+
+    class Block0(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.t = 0
+
+        def forward(self, hidden_states, encoder_hidden_states):
+            out = h1s[self.t]
+            self.t += 1
+            return out, (encoder_hidden_states.float() + 0.25).bfloat16()
+
+    class Block1(torch.nn.Module):
+        def forward(self, hidden_states, encoder_hidden_states):
+            return (hidden_states.float() * 1.5).bfloat16(), (encoder_hidden_states.float() * 0.5).bfloat16()
+
+    blocks = fbc.CachedTransformerBlocks(torch.nn.ModuleList([Block0(), Block1()]))
+    hits = []
+    with fbc.cache_context(fbc.create_cache_context(**kw)):
+        for t in range(h0s.shape[0]):
+            before = fbc.get_current_cache_context().get_buffer("first_hidden_states_residual")
+            out, enc_out = blocks(h0s[t], enc)
+            after = fbc.get_current_cache_context().get_buffer("first_hidden_states_residual")
+            hits.append(after is before and before is not None)
+            if f"{case}_out" in g:
+                assert torch.equal(out, bf16_from_bits(g[f"{case}_out"][t])), f"step {t}: hidden states differ"
+            if f"{case}_enc_out" in g:
+                assert torch.equal(enc_out, bf16_from_bits(g[f"{case}_enc_out"][t])), f"step {t}: encoder states differ"
+    assert hits == list(g[f"{case}_hit"])
+
+
+def test_full_size_sums_and_bandwidth_shape():
+    """FLUX-sized residual (4096 x 3072 bf16): sums agree with a torch fp64 evaluation."""
+    n, c = 4096, 3072
+    g = torch.Generator(device="cuda").manual_seed(0)
+    h0 = torch.randn(1, n, c, generator=g, device="cuda").bfloat16()
+    h1 = (h0.float() + 0.2 * torch.randn(1, n, c, generator=g, device="cuda")).bfloat16()
+    prev = (0.2 * torch.randn(1, n, c, generator=g, device="cuda")).bfloat16()
+    cur, res = _abi_residual_diff(h1, h0, prev)
+    want_cur = h1 - h0
+    assert torch.equal(cur, want_cur)
+    sd = (prev - want_cur).abs().double().sum().item()
+    sp = prev.abs().double().sum().item()
+    np.testing.assert_allclose(res[0], sd, rtol=1e-5)
+    np.testing.assert_allclose(res[1], sp, rtol=1e-5)

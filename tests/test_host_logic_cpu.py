@@ -1,0 +1,180 @@
+"""Host-side logic without a GPU: the exchange plan against the reference's all-to-all layout,
+the mesh helper and the shard helpers over gloo (world size 2 and 4), and the cache's step
+bookkeeping."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import cp_attention_oracle as O
+
+
+def _simulate_plan(U, R, H, s, d=8):
+    """Move numpy data exactly as CpPlan.push_jobs prescribes and return, per rank, the staged
+    (q, k, v) as [b, hl, chunks*s, d] in chunk-slot order."""
+    from paraattention_b200._cp_engine import CpPlan
+
+    W = U * R
+    rng = np.random.default_rng(U * 100 + R)
+    local = {n: [rng.standard_normal((1, H, s, d)).astype(np.float32) for _ in range(W)] for n in "qkv"}
+    hl = H // U
+    stage = {n: [[None] * (U if n == "q" else W) for _ in range(W)] for n in "qkv"}
+    for g in range(W):
+        plan = CpPlan(U, R, g % U, g // U, H)
+        assert plan.rank == g
+        for job in plan.push_jobs():
+            stage[job.tensor][job.dest][job.chunk] = local[job.tensor][g][:, job.head0:job.head0 + job.heads]
+    for n in "qkv":
+        for g in range(W):
+            assert all(x is not None for x in stage[n][g]), "a staging slot was never filled"
+    return local, stage, hl
+
+
+@pytest.mark.parametrize("U,R", [(2, 1), (1, 2), (2, 2), (4, 2), (2, 4), (8, 1), (1, 8)])
+def test_plan_reproduces_reference_layout(U, R):
+    H, s = 8, 5
+    W = U * R
+    local, stage, hl = _simulate_plan(U, R, H, s)
+    from paraattention_b200._cp_engine import CpPlan
+
+    for r in range(R):
+        group = [r * U + u for u in range(U)]
+        # query side: staged Q of rank (u, r) == reference's Ulysses input all-to-all
+        want_q = O.ulysses_input_all_to_all([local["q"][g] for g in group])
+        for u, g in enumerate(group):
+            got = np.concatenate(stage["q"][g], axis=2)
+            np.testing.assert_array_equal(got, want_q[u])
+    # key side: rank (u, r) must see head slice u of every rank's K/V exactly once
+    for g in range(W):
+        u = g % U
+        for n in "kv":
+            got = np.concatenate(stage[n][g], axis=2)
+            want = np.concatenate([local[n][src][:, u * hl:(u + 1) * hl] for src in range(W)], axis=2)
+            np.testing.assert_array_equal(got, want)
+    # output side: every (rank, head) slot of every rank is written by exactly one q-chunk owner
+    writes = {}
+    for g in range(W):
+        plan = CpPlan(U, R, g % U, g // U, H)
+        for c in range(U):
+            dest, head_off = plan.out_dest(c)
+            for h in range(hl):
+                key = (dest, head_off + h)
+                assert key not in writes
+                writes[key] = g
+        assert sorted(plan.out_writers()) == sorted(r_ * U + u_ for r_ in [g // U] for u_ in range(U))
+    assert len(writes) == W * H
+
+
+def test_plan_attention_equals_oracle_unified():
+    """Attention over the staged tensors (keys in chunk-slot order) equals the oracle's
+    Ulysses-around-ring result: the fused exchange computes the same function."""
+    U, R, H, s = 2, 2, 4, 6
+    local, stage, hl = _simulate_plan(U, R, H, s)
+    W = U * R
+    want = O.unified_attention(local["q"], local["k"], local["v"], ulysses=U, ring=R)
+    got = [np.zeros_like(local["q"][0]) for _ in range(W)]
+    from paraattention_b200._cp_engine import CpPlan
+
+    for g in range(W):
+        plan = CpPlan(U, R, g % U, g // U, H)
+        k = np.concatenate(stage["k"][g], axis=2)
+        v = np.concatenate(stage["v"][g], axis=2)
+        for c in range(U):
+            out, _ = O.sdpa_with_lse(stage["q"][g][c], k, v)
+            dest, head_off = plan.out_dest(c)
+            got[dest][:, head_off:head_off + hl] = out
+    for g in range(W):
+        np.testing.assert_allclose(got[g], want[g], atol=1e-5)
+
+
+def _gloo_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from paraattention_b200 import primitives as DP
+    from paraattention_b200.context_parallel import init_context_parallel_mesh
+    import paraattention_b200 as pa
+
+    out = {}
+    mesh = init_context_parallel_mesh("cpu", max_ring_dim_size=2)
+    out["mesh_shape"] = tuple(mesh.mesh.shape)
+    out["names"] = mesh.mesh_dim_names
+    out["u"], out["r"] = DP.get_rank(mesh["ulysses"]), DP.get_rank(mesh["ring"])
+    x = torch.arange(world * 6, dtype=torch.float32).reshape(1, world * 3, 2)
+    mine = DP.get_assigned_chunk(x, dim=-2)
+    out["chunk_ok"] = torch.equal(mine, x.chunk(world, dim=-2)[rank])
+    out["gather_ok"] = torch.equal(DP.get_complete_tensor(mine, dim=-2), x)
+    try:
+        DP.get_assigned_chunk(torch.zeros(1, world * 3 + 1, 2), dim=-2)
+        out["div_assert"] = False
+    except AssertionError:
+        out["div_assert"] = True
+    # a multi-rank attention call on CPU tensors must fail loudly, never fall back
+    q = torch.zeros(1, world, 4, 128, dtype=torch.bfloat16)
+    try:
+        pa.ulysses_attn_func(q, q, q)
+        out["cpu_refused"] = False
+    except (AssertionError, NotImplementedError, RuntimeError):
+        out["cpu_refused"] = True
+    try:
+        pa.ring_attn_func(q, q, q, attn_mask=torch.ones(4, 4, dtype=torch.bool))
+        out["mask_assert"] = False
+    except AssertionError:
+        out["mask_assert"] = True
+    mode = pa.UnifiedAttnMode(mesh)
+    out["mode_groups"] = (mode._ulysses_mesh is not None, mode._ring_mesh is not None)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, out)
+    if rank == 0:
+        ret.put(gathered)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_mesh_and_shard_helpers_over_gloo(world):
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, world, 29800 + world, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = ret.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+    ring = 2
+    uly = world // ring
+    for rank, o in enumerate(res):
+        assert o["mesh_shape"] == (1, ring, uly) and o["names"] == ("batch", "ring", "ulysses")
+        assert (o["u"], o["r"]) == (rank % uly, rank // uly)  # ulysses is the fastest mesh dim
+        assert o["chunk_ok"] and o["gather_ok"] and o["div_assert"] and o["cpu_refused"] and o["mask_assert"]
+        assert o["mode_groups"] == (True, True)
+
+
+def test_cache_context_step_bookkeeping():
+    from paraattention_b200.first_block_cache import utils as fbc
+
+    ctx = fbc.create_cache_context(residual_diff_threshold=0.1, warmup_steps=2)
+    with fbc.cache_context(ctx):
+        assert fbc.get_current_cache_context() is ctx
+        for step in range(4):
+            fbc.mark_step_begin()
+            assert ctx.get_current_step() == step
+            assert fbc.is_in_warmup() == (step < 2)
+    assert fbc.get_current_cache_context() is None
+    # alternate cache: the flag flips every call starting from True, steps count on the non-alter call
+    ctx = fbc.create_cache_context(enable_alter_cache=True, alter_residual_diff_threshold=0.3,
+                                   residual_diff_threshold=0.1, num_inference_steps=10, slg_layers=[1], slg_end=0.5)
+    seen = []
+    for _ in range(4):
+        ctx.mark_step_begin()
+        ctx.set_buffer("x", len(seen))
+        seen.append((ctx.is_alter_cache, ctx.executed_steps, ctx.get_residual_diff_threshold(),
+                     ctx.slg_should_skip_block(1)))
+    assert seen == [(False, 1, 0.1, False), (True, 1, 0.3, True), (False, 2, 0.1, False), (True, 2, 0.3, True)]
+    assert set(ctx.buffers) == {"x", "x_alter"}
+    with pytest.raises(NotImplementedError):
+        fbc.create_cache_context(enable_taylorseer=True)
+    with pytest.raises(AssertionError):
+        fbc.mark_step_begin()

@@ -1,0 +1,108 @@
+"""The numpy oracle against fixtures produced by the reference itself (tests/golden/make_golden.py)."""
+import numpy as np
+import pytest
+
+from oracle import cp_attention_oracle as O
+
+
+def _f32(bits):
+    return O.bf16_bits_to_f32(bits)
+
+
+@pytest.fixture(scope="module")
+def w2(golden_dir):
+    return np.load(golden_dir / "cp_attention_w2.npz")
+
+
+@pytest.fixture(scope="module")
+def w4(golden_dir):
+    return np.load(golden_dir / "cp_attention_w4.npz")
+
+
+def _shards(x, world):
+    return np.split(x, world, axis=-2)
+
+
+def test_single_device_sdpa(w2):
+    q, k, v = _f32(w2["q"]), _f32(w2["k"]), _f32(w2["v"])
+    out, lse = O.sdpa_with_lse(q, k, v)
+    np.testing.assert_allclose(out, w2["single"], atol=2e-6, rtol=1e-5)
+    s = np.matmul(q.astype(np.float64), np.swapaxes(k.astype(np.float64), -1, -2)) / np.sqrt(128.0)
+    ref_lse = np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)
+    np.testing.assert_allclose(lse, ref_lse, atol=1e-5)
+
+
+@pytest.mark.parametrize("name,causal", [("ulysses", False), ("ulysses_causal", True)])
+def test_ulysses_world2(w2, name, causal):
+    q, k, v = (_shards(_f32(w2[n]), 2) for n in ("q", "k", "v"))
+    outs = O.ulysses_attention(q, k, v, is_causal=causal)
+    np.testing.assert_allclose(np.stack(outs), w2[name], atol=2e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name,causal", [("ring", False), ("ring_causal", True)])
+def test_ring_world2(w2, name, causal):
+    q, k, v = (_shards(_f32(w2[n]), 2) for n in ("q", "k", "v"))
+    outs = O.ring_attention(q, k, v, is_causal=causal)
+    np.testing.assert_allclose(np.stack(outs), w2[name], atol=2e-6, rtol=1e-5)
+
+
+def test_short_kv_world2(w2):
+    q, k, v = (_shards(_f32(w2[n]), 2) for n in ("q2", "k2", "v2"))
+    np.testing.assert_allclose(np.stack(O.ring_attention(q, k, v)), w2["ring_short_kv"], atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(np.stack(O.ulysses_attention(q, k, v)), w2["ulysses_short_kv"], atol=2e-6, rtol=1e-5)
+
+
+def test_unified_and_ring_world4(w2, w4):
+    q, k, v = (_shards(_f32(w2[n]), 4) for n in ("q", "k", "v"))
+    uni = O.unified_attention(q, k, v, ulysses=2, ring=2)
+    np.testing.assert_allclose(np.stack(uni), w4["unified_2x2"], atol=2e-6, rtol=1e-5)
+    ring = O.ring_attention(q, k, v)
+    np.testing.assert_allclose(np.stack(ring), w4["ring4"], atol=2e-6, rtol=1e-5)
+
+
+def test_sharded_equals_single_device(w2):
+    # the reference's own pinned contract (tests/test_interface.py:70): shard r == chunk r of single-device SDPA
+    q, k, v = (_shards(_f32(w2[n]), 4) for n in ("q", "k", "v"))
+    full = np.concatenate(O.unified_attention(q, k, v, ulysses=2, ring=2), axis=-2)
+    np.testing.assert_allclose(full, w2["single"], atol=1e-5)
+
+
+def test_merge_is_order_free():
+    rng = np.random.default_rng(0)
+    q = rng.standard_normal((1, 2, 16, 8)).astype(np.float32)
+    k = rng.standard_normal((1, 2, 48, 8)).astype(np.float32)
+    v = rng.standard_normal((1, 2, 48, 8)).astype(np.float32)
+    full, full_lse = O.sdpa_with_lse(q, k, v)
+    parts = [O.sdpa_with_lse(q, k[:, :, i:i + 16], v[:, :, i:i + 16]) for i in (32, 0, 16)]
+    out, lse = parts[0]
+    for bo, bl in parts[1:]:
+        out, lse = O.merge_out_lse(out, lse, bo, bl)
+    np.testing.assert_allclose(out, full, atol=1e-5)
+    np.testing.assert_allclose(lse, full_lse, atol=1e-5)
+
+
+def test_bf16_round_matches_torch():
+    import torch
+
+    x = np.random.default_rng(1).standard_normal(4096).astype(np.float32) * 100
+    x[:4] = [0.0, -0.0, 1.00390625, 3.3895314e38]
+    want = torch.from_numpy(x).bfloat16().float().numpy()
+    np.testing.assert_array_equal(O.bf16_round(x), want)
+    np.testing.assert_array_equal(O.bf16_bits_to_f32(O.f32_to_bf16_bits(x)), want)
+
+
+@pytest.mark.parametrize("case,kw", [
+    ("thr008", dict(residual_diff_threshold=0.08)),
+    ("thr003_warm2", dict(residual_diff_threshold=0.03, warmup_steps=2)),
+    ("thr02_ds2", dict(residual_diff_threshold=0.2, downsample_factor=2)),
+    ("thr0", dict(residual_diff_threshold=0.0)),
+])
+def test_fbcache_decisions(golden_dir, case, kw):
+    g = np.load(golden_dir / "fbcache_steps.npz")
+    h0, h1 = _f32(g["h0"]), _f32(g["h1"])
+    state = O.FbcStateOracle(**kw)
+    hits = []
+    for t in range(h0.shape[0]):
+        first_residual = O.bf16_round(h1[t] - h0[t])  # bf16 tensor subtraction, utils.py:359
+        hits.append(state.step(first_residual))
+    assert hits == list(g[f"{case}_hit"])
