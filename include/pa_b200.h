@@ -92,6 +92,8 @@ int pa_attn_fwd(const pa_attn_args* args, void* stream);
  * lse likewise if lse[c] != NULL. After a CTA has stored a tile for chunk c it adds 1 to
  * done_flag[c] (system-scope release) when that pointer is non-NULL.
  * ---------------------------------------------------------------------------------------- */
+struct pa_cp_push_args;
+
 typedef struct pa_cp_attn_args {
     const void* q_stage;     /* [n_q_chunks, batch, heads, q_rows, 128] */
     const void* k_stage;     /* [n_kv_chunks, batch, heads, kv_rows, 128] */
@@ -111,6 +113,12 @@ typedef struct pa_cp_attn_args {
     uint32_t* done_flag[PA_MAX_CHUNKS];
     int32_t* status;
     uint64_t wait_limit_ns;
+    /* Fused exchange (may be NULL): the first fused_push->ctas_per_dest CTAs of this launch
+     * (capped by the grid size and 128) perform the pushes described by *fused_push before they
+     * take up attention tiles, and add 1 each to every destination's counter. The consumers'
+     * flag_expect must therefore grow by that CTA count per call. The host struct is read
+     * during the call only. */
+    const struct pa_cp_push_args* fused_push;
 } pa_cp_attn_args;
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);
@@ -121,6 +129,12 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);
  * No counterpart in the reference. */
 int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo, int pv_split, void* stream);
 
+/* Test hook: pa_attn_fwd whose first CTA records clock64() stamps of its pipeline phases for
+ * the first `steps` key/value tiles into stamps[3][steps][8] (roles: softmax of query tile 0,
+ * softmax of query tile 1, MMA issuer). Used to read the kernel's timeline without a
+ * profiler. No counterpart in the reference. */
+int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Exchange. Replaces the NCCL all_to_all_single calls of _sdpa_input_all_to_all /
  * _sdpa_output_all_to_all (src/para_attn/para_attn_interface.py:52-87, through
@@ -129,6 +143,10 @@ int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo
  * tensor to dst (normally a peer GPU's mapped staging buffer) with the given element
  * strides; when all jobs of a destination are stored, flag[dest] on that destination is
  * increased by ctas_per_dest in total (each CTA adds 1 with a system-scope release).
+ * pa_cp_push is the stand-alone launch (grid ctas_per_dest x n_dest); the same description
+ * can ride inside pa_cp_attn_fwd (pa_cp_attn_args.fused_push), which is what multi-GPU runs
+ * use: a separate push kernel is not guaranteed to get SMs while attention CTAs that wait
+ * for it fill the device.
  * ---------------------------------------------------------------------------------------- */
 #define PA_MAX_PUSH_JOBS 24
 
@@ -148,7 +166,7 @@ typedef struct pa_cp_push_args {
     int32_t n_dest;
     uint32_t* flag[PA_MAX_CHUNKS];
     int32_t ctas_per_dest;
-    int32_t pad_;
+    int32_t first_dest;      /* destinations are served in the order first_dest, first_dest + 1, ... */
 } pa_cp_push_args;
 
 int pa_cp_push(const pa_cp_push_args* args, void* stream);

@@ -4,14 +4,13 @@ Replaces, for one attention call on a (ring x ulysses) mesh, the reference's seq
 NCCL all_to_all -> per-step SDPA + K/V rotation + out/LSE merge -> all_to_all
 (src/para_attn/para_attn_interface.py:52-119, 162-239, 445-479) by
 
-  1. ``pa_cp_push``   every rank stores the head-slices of its local Q/K/V shard that
-                      another rank needs directly into that rank's staging buffer (peer
-                      stores) and bumps an arrival counter there;
-  2. ``pa_cp_attn_fwd`` one attention launch per rank that consumes the K/V chunks in arrival
-                      order (own shard first) while later chunks are still in flight, keeps
-                      the running softmax state on chip, and writes every output tile
-                      straight into the buffer of the rank that owns those query rows;
-  3. a bounded, stream-ordered wait until all tiles owed to this rank have arrived.
+  1. ONE launch of ``pa_cp_attn_fwd`` per rank. Its leading CTAs first store the head-slices
+     of the local Q/K/V shard that other ranks need directly into those ranks' staging
+     buffers (peer stores over NVLink) and bump arrival counters there; every CTA then
+     computes attention, consuming the K/V chunks in arrival order (own shard first) while
+     later chunks are still in flight, keeping the running softmax state on chip, and
+     writing every output tile straight into the buffer of the rank that owns those rows;
+  2. a bounded, stream-ordered wait until all tiles owed to this rank have arrived.
 
 ``CpPlan`` is the pure-python description of who sends what where; it is what the CPU tests
 exercise. ``CpEngine`` owns the symmetric-memory workspace (allocated once per group and
@@ -182,7 +181,16 @@ def _fix(x: torch.Tensor) -> torch.Tensor:
 
 
 def launch_push(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int, stream: int) -> None:
-    """pa_cp_push of this rank's shard into every consumer's staging buffer (parity ``par``)."""
+    """Stand-alone pa_cp_push of this rank's shard into every consumer's staging buffer
+    (parity ``par``). Multi-GPU runs use the fused form instead (``build_push_args`` handed
+    to ``launch_attention``); this one serves one-GPU emulation, where all pushes must be
+    complete before any attention launch starts."""
+    pa = build_push_args(plan, ws, par, q, k, v, ctas)
+    L.check(L.load().pa_cp_push(C.byref(pa), stream))
+
+
+def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int) -> "L.CpPushArgs":
+    """Describe the pushes of this rank: which head-slice of q/k/v goes to which rank's buffer."""
     lay = ws.layout
     B, H, sq, D = q.shape
     skv = k.shape[2]
@@ -212,13 +220,22 @@ def launch_push(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int, strea
         # counter slot on the destination = my plan rank (= chunk slot of my K/V there)
         pa.flag[d] = ws.peer[d] + lay.off_arrive[par] + 4 * plan.rank
     pa.ctas_per_dest = ctas
-    L.check(L.load().pa_cp_push(C.byref(pa), stream))
+    pa.first_dest = plan.rank  # own buffer first, then the peers in ring order
+    return pa
+
+
+def fused_push_ctas(plan: CpPlan, B: int, sq: int, ctas: int) -> int:
+    """How many leading CTAs of the attention grid push (the library applies the same cap)."""
+    grid = ((sq + 255) // 256) * plan.local_heads * B * plan.ulysses
+    return max(1, min(ctas, grid, 128))
 
 
 def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
-                     arrive_expect: int, wait_ns: int, stream: int, out_local: Optional[torch.Tensor]) -> None:
+                     arrive_expect: int, wait_ns: int, stream: int, out_local: Optional[torch.Tensor],
+                     push: Optional["L.CpPushArgs"] = None) -> None:
     """pa_cp_attn_fwd for this rank. ``out_local`` (ring-only meshes) receives the result in
-    place; otherwise tiles go to the owners' output staging buffers."""
+    place; otherwise tiles go to the owners' output staging buffers. With ``push`` the launch
+    also performs this rank's part of the exchange (fused form)."""
     lay = ws.layout
     B, H, sq, D = shape
     hl = plan.local_heads
@@ -249,6 +266,7 @@ def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.
     a.flag_expect = arrive_expect
     a.status = base + lay.off_status
     a.wait_limit_ns = wait_ns
+    a.fused_push = C.addressof(push) if push is not None else None
     L.check(L.load().pa_cp_attn_fwd(C.byref(a), stream))
 
 
@@ -282,7 +300,6 @@ class CpEngine:
         self.ws: Optional[Workspace] = None
         self.hdl = None
         self.state = CallState()
-        self.side_stream = torch.cuda.Stream(device=device)
         # group rank of mesh coordinate (u, r): the mesh may order ranks differently from r*U+u
         me = torch.tensor([u, r], dtype=torch.int64, device=device)
         coords = [torch.empty_like(me) for _ in range(self.world)]
@@ -337,22 +354,16 @@ class CpEngine:
         main = torch.cuda.current_stream(self.device)
         q, k, v = _fix(q), _fix(k), _fix(v)
 
-        # 1. push on a side stream, so that it runs beside the attention kernel
-        st.arrive_expect[par] += ctas
-        ev_in = torch.cuda.Event()
-        ev_in.record(main)
-        self.side_stream.wait_event(ev_in)
-        launch_push(plan, ws, par, q, k, v, ctas, self.side_stream.cuda_stream)
-        ev_push = torch.cuda.Event()
-        ev_push.record(self.side_stream)
-
-        # 2. attention
+        # 1 + 2. one launch: the leading CTAs push this rank's shard to its consumers, all CTAs
+        # compute attention over the chunks as they arrive
+        n_push = fused_push_ctas(plan, B, sq, ctas)
+        st.arrive_expect[par] += n_push
+        push = build_push_args(plan, ws, par, q, k, v, n_push)
         out_local = None
         if self.ulysses == 1:
             out_local = torch.empty((B, sq, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
         launch_attention(plan, ws, par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par], wait_ns,
-                         main.cuda_stream, out_local)
-        main.wait_event(ev_push)  # inputs may be reused only after they were sent
+                         main.cuda_stream, out_local, push)
         if out_local is not None:
             return out_local
 

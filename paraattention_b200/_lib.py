@@ -55,6 +55,7 @@ class CpAttnArgs(C.Structure):
         ("flag_expect", C.c_uint32),
         ("done_flag", C.c_void_p * PA_MAX_CHUNKS),
         ("status", C.c_void_p), ("wait_limit_ns", C.c_uint64),
+        ("fused_push", C.c_void_p),
     ]
 
 
@@ -75,7 +76,7 @@ class CpPushArgs(C.Structure):
         ("jobs", PushJob * PA_MAX_PUSH_JOBS),
         ("n_jobs", C.c_int32), ("n_dest", C.c_int32),
         ("flag", C.c_void_p * PA_MAX_CHUNKS),
-        ("ctas_per_dest", C.c_int32), ("pad_", C.c_int32),
+        ("ctas_per_dest", C.c_int32), ("first_dest", C.c_int32),
     ]
 
 

@@ -6,9 +6,13 @@
 //   warps 4-7  softmax for query tile 1
 //   warp  8    MMA issuer (one thread): S_t = Q_t K_j^T into TMEM, O_t += P_t V_j from TMEM
 //   warp  9    TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
+//   warps 10-11 idle; they complete the control warpgroup that gives its registers away
 // TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512);
 // P_t (bf16/f16, 64 columns) overwrites the front of S_t and is the TMEM A operand of P V.
 // While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs.
+//
+// In context-parallel runs the same launch also performs the exchange (see the fused push
+// below): one kernel per attention call and rank, no collective library call on the path.
 //
 // Key/value rows come as a list of equally sized chunks (one per source rank in context
 // parallel runs, one in total otherwise); running max / sum / O stay on chip across
@@ -22,6 +26,7 @@
 
 #include "../../include/pa_b200.h"
 #include "pa_ptx.cuh"
+#include "cp_exchange_sm100.cuh"
 
 namespace pa {
 
@@ -34,11 +39,36 @@ constexpr int kStages = 2;
 constexpr int kSoftmaxWarps = 8;
 constexpr int kMmaWarp = 8;
 constexpr int kTmaWarp = 9;
-constexpr int kAttnThreads = 320;
+constexpr int kAttnThreads = 384;  // 2 softmax warpgroups + 1 control warpgroup (MMA, TMA, 2 idle warps)
+#ifndef PA_REGS_SOFTMAX
+#define PA_REGS_SOFTMAX 200
+#endif
+#ifndef PA_REGS_CONTROL
+#define PA_REGS_CONTROL 104
+#endif
+constexpr int kRegsSoftmax = PA_REGS_SOFTMAX;
+constexpr int kRegsControl = PA_REGS_CONTROL;
+// The CTA is launched with 168 registers per thread (the cap for 384 threads). Each scheduler
+// partition holds one warp of each warpgroup, so what the two softmax warps gain must be
+// covered by what the control warp gives up - otherwise setmaxnreg.inc would wait forever.
+static_assert(2 * kRegsSoftmax + kRegsControl <= 3 * 168, "setmaxnreg budget exceeds the launch allocation");
+static_assert(kRegsSoftmax % 8 == 0 && kRegsControl % 8 == 0, "setmaxnreg counts are multiples of 8");
+// The MMA issuer must keep ahead of the tensor core (64 cycles per 128x128x16 MMA): its k-step
+// loops are unrolled so that an issue costs a handful of instructions.
+#if defined(PA_ROLLED_MMA) && PA_ROLLED_MMA
+#define PA_MMA_UNROLL _Pragma("unroll 1")
+#else
+#define PA_MMA_UNROLL _Pragma("unroll")
+#endif
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColO0 = 256;
 // log2-domain growth of the running row maximum that is tolerated before O is rescaled
 constexpr float kRescaleThreshold = 8.0f;
+// of every 8 pairs of probabilities, how many are exponentiated with the FMA-pipe polynomial
+#ifndef PA_POLY_PAIRS_OF_8
+#define PA_POLY_PAIRS_OF_8 0
+#endif
+constexpr int kPolyPairsOf8 = PA_POLY_PAIRS_OF_8;
 
 struct AttnParams {
     int batch, heads;
@@ -59,7 +89,17 @@ struct AttnParams {
     float* dbg_s;      // raw S of CTA 0: [tile][kv tile][row][col]
     int v_lbo, v_sbo;  // B descriptor of V (bytes)
     int pv_split;      // 1: issue P V as two N=64 MMAs
+    long long* dbg_t;  // clock64 stamps of CTA 0: [role 0..2][step][8]; roles: softmax 0, softmax 1, MMA issuer
+    int dbg_steps;
 };
+
+template <bool kDebug>
+__device__ __forceinline__ void dbg_stamp(const AttnParams& p, int role, int step, int slot, bool who) {
+    if (kDebug) {
+        if (p.dbg_t != nullptr && blockIdx.x == 0 && who && step < p.dbg_steps)
+            p.dbg_t[(static_cast<size_t>(role) * p.dbg_steps + step) * 8 + slot] = clock64();
+    }
+}
 
 struct AttnSmemCtl {
     uint64_t q_full;
@@ -79,7 +119,8 @@ static_assert(sizeof(AttnSmemCtl) <= 256, "control block too large");
 template <bool kBF16, bool kDebug>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p,
+                const __grid_constant__ PushParams push) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -147,6 +188,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int n_tiles = tiles_per_chunk * p.n_kv_chunks;
     const uint64_t pipe_limit = p.wait_ns + 1000000000ull;
 
+    // Fused exchange: the leading CTAs of the grid (always resident in the first wave, and
+    // waiting for nobody) first store this rank's Q/K/V head-slices into the staging buffers
+    // of the ranks that consume them - own buffer first, then the peers in ring order - and
+    // only then take up their attention tiles. Every other CTA starts computing at once and
+    // meets a chunk only when it needs it.
+    if (push.n_push_ctas > 0 && static_cast<int>(blockIdx.x) < push.n_push_ctas) {
+        for (int di = 0; di < push.n_dest; ++di) {
+            int dest = push.first_dest + di;
+            if (dest >= push.n_dest) dest -= push.n_dest;
+            push_to_dest(push, dest, blockIdx.x, push.n_push_ctas);
+        }
+    }
+
+    // Registers move from the control warpgroup to the softmax warpgroups (per scheduler
+    // partition: 2 x 200 + 112 registers x 32 lanes fill the 16K file).
+    // (each role's code is dominated by its own setmaxnreg so that the register allocator
+    // budgets the three regions separately)
+    if (warp >= kSoftmaxWarps) setmaxnreg_dec<kRegsControl>();
     if (warp == kTmaWarp) {
         // =============================== TMA producer ======================================
         if (lane == 0) {
@@ -229,30 +288,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t v_sbo = kDebug ? static_cast<uint32_t>(p.v_sbo) : 1024u;
             const bool pv_split = kDebug ? (p.pv_split != 0) : false;
 
+            // Descriptors differ from a per-operand base only in the start-address field (units
+            // of 16 bytes).
+            const uint64_t dq0 = smem_desc_sw128(sQ, 16, 1024);
+            const uint64_t dk0 = smem_desc_sw128(sK, 16, 1024);
+            const uint64_t dv0 = smem_desc_sw128(sV, v_lbo, v_sbo);
             auto issue_qk = [&](int t, int st) {
-#pragma unroll
+                const uint64_t a0 = dq0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
+                const uint64_t b0 = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
+                const uint32_t d = tmem + kColS0 + t * kTileN;
+                PA_MMA_UNROLL
                 for (int ks = 0; ks < kHeadDim / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-                    const uint64_t a = smem_desc_sw128(sQ + t * kTileBytes + off, 16, 1024);
-                    const uint64_t b = smem_desc_sw128(sK + st * kTileBytes + off, 16, 1024);
-                    tc_mma_ss(tmem + kColS0 + t * kTileN, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                    const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+                    tc_mma_ss(d, a0 + off, b0 + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int t, int st, bool acc) {
-#pragma unroll
+                const uint64_t b0 = dv0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
+                const uint32_t a0 = tmem + kColS0 + t * kTileN;
+                const uint32_t d = tmem + kColO0 + t * kHeadDim;
+                PA_MMA_UNROLL
                 for (int ks = 0; ks < kTileN / 16; ++ks) {
-                    const uint32_t vaddr = sV + st * kTileBytes + ks * 16 * 128;
-                    const uint32_t a = tmem + kColS0 + t * kTileN + ks * 8;
+                    const uint64_t b = b0 + static_cast<uint64_t>((ks * 16 * 128) >> 4);
                     const uint32_t accum = (acc || ks > 0) ? 1u : 0u;
                     if (!pv_split) {
-                        tc_mma_ts(tmem + kColO0 + t * kHeadDim, a,
-                                  smem_desc_sw128(vaddr, v_lbo, v_sbo), idesc_pv, accum);
+                        tc_mma_ts(d, a0 + ks * 8, b, idesc_pv, accum);
                     } else {
-                        tc_mma_ts(tmem + kColO0 + t * kHeadDim, a,
-                                  smem_desc_sw128(vaddr, v_lbo, v_sbo), idesc_pv64, accum);
-                        tc_mma_ts(tmem + kColO0 + t * kHeadDim + 64, a,
-                                  smem_desc_sw128(vaddr + kHalfBytes, v_lbo, v_sbo), idesc_pv64,
-                                  accum);
+                        tc_mma_ts(d, a0 + ks * 8, b, idesc_pv64, accum);
+                        tc_mma_ts(d + 64, a0 + ks * 8, b + static_cast<uint64_t>(kHalfBytes >> 4), idesc_pv64, accum);
                     }
                 }
             };
@@ -283,18 +346,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 if (!ok) break;
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
+                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 0, true);
                     ok = mbar_wait(smem_u32(&ctl->p_full[t]), j & 1, s_abort, p.status, pipe_limit,
                                    PA_DEV_TIMEOUT_PIPE);
                     if (!ok) break;
+                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 1, true);
                     tc_fence_after();
                     issue_pv(t, st, j > 0);
                     tc_commit(smem_u32(&ctl->o_done[t]));
                     if (t == 1) tc_commit(smem_u32(&ctl->v_empty[st]));
+                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 2, true);
                     if (more) {
                         issue_qk(t, stn);
                         tc_commit(smem_u32(&ctl->s_full[t]));
                         if (t == 1) tc_commit(smem_u32(&ctl->k_empty[stn]));
                     }
+                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 3, true);
                 }
             }
             if (!ok) {
@@ -305,8 +372,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 mbar_wait(smem_u32(&ctl->teardown), 0, no_abort, nullptr, 100000000ull, 0);
             }
         }
-    } else {
+    } else if (warp < kSoftmaxWarps) {
         // =============================== softmax + epilogue ================================
+        setmaxnreg_inc<kRegsSoftmax>();
         const int t = warp >> 2;
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
@@ -325,8 +393,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
             for (int tk = 0; tk < tiles_per_chunk; ++tk, ++j) {
                 const int valid = min(kTileN, p.kv_rows - tk * kTileN);
+                const bool stamper = (quarter == 0 && lane == 0);
+                dbg_stamp<kDebug>(p, t, j, 0, stamper);
                 ok = mbar_wait(bs, j & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE);
                 if (!ok) break;
+                dbg_stamp<kDebug>(p, t, j, 1, stamper);
                 tc_fence_after();
                 uint32_t s[4][32];
 #pragma unroll
@@ -334,6 +405,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tc_wait_ld();
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld_fence(s[c]);
+                dbg_stamp<kDebug>(p, t, j, 2, stamper);
                 if (kDebug && p.dbg_s != nullptr && blockIdx.x == 0) {
                     float* d = p.dbg_s + ((static_cast<size_t>(t) * n_tiles + j) * 128 + row_in_tile) * 128;
 #pragma unroll
@@ -351,9 +423,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 float mx[4];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    mx[c] = __uint_as_float(s[c][0]);
+                    mx[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
 #pragma unroll
-                    for (int i = 1; i < 32; ++i) mx[c] = fmaxf(mx[c], __uint_as_float(s[c][i]));
+                    for (int i = 2; i < 32; i += 2)
+                        mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
                 }
                 const float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_ref);
                 const bool grow = (m_new - m_ref) * sl > kRescaleThreshold;
@@ -380,7 +453,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     }
                 }
                 const float neg = -m_ref * sl;
-                float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                dbg_stamp<kDebug>(p, t, j, 3, stamper);
+                // p = 2^(s*sl - m*sl): packed fp32x2 arithmetic; kPolyPairsOf8 of every 8 element
+                // pairs take the FMA-pipe polynomial, the rest the special-function unit, so that
+                // neither pipe alone bounds the softmax.
+                const float2 sl2 = make_float2(sl, sl);
+                const float2 neg2 = make_float2(neg, neg);
+                float2 ls[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
+                                make_float2(0.f, 0.f)};
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t pk[32];
@@ -389,18 +469,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         const int c = half * 2 + cc;
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
-                            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c][i]), sl, neg));
-                            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c][i + 1]), sl, neg));
-                            ls[c] += p0 + p1;
-                            pk[cc * 16 + (i >> 1)] = kBF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+                            const float2 x = __ffma2_rn(
+                                make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sl2, neg2);
+                            float2 e;
+                            if (((i >> 1) & 7) < kPolyPairsOf8) {
+                                e = exp2_poly2(x);
+                            } else {
+                                e.x = ex2_approx(x.x);
+                                e.y = ex2_approx(x.y);
+                            }
+                            ls[c] = __fadd2_rn(ls[c], e);
+                            pk[cc * 16 + (i >> 1)] = kBF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
                         }
                     }
                     tmem_st32(tS + half * 32, pk);
                 }
-                l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                {
+                    const float2 a = __fadd2_rn(__fadd2_rn(ls[0], ls[1]), __fadd2_rn(ls[2], ls[3]));
+                    l_sum += a.x + a.y;
+                }
+                dbg_stamp<kDebug>(p, t, j, 4, stamper);
                 tc_wait_st();
                 tc_fence_before();
                 mbar_arrive(bp);
+                dbg_stamp<kDebug>(p, t, j, 5, stamper);
             }
         }
         if (ok) ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE);

@@ -16,9 +16,11 @@ struct PushParams {
     int n_jobs;
     uint32_t* flag[PA_MAX_CHUNKS];  // per destination, in that destination's memory
     int n_dest;
+    int first_dest;   // destinations are served in the order first_dest, first_dest+1, ... (mod n_dest)
+    int n_push_ctas;  // fused form only: how many leading CTAs of the attention grid push
 };
 
-constexpr int kPushThreads = 256;  // small enough to share an SM with an attention CTA
+constexpr int kPushThreads = 256;  // stand-alone kernel: small enough to share an SM
 constexpr int kPushUnroll = 4;     // independent 16-byte loads in flight per thread
 
 __device__ __forceinline__ void push_row_ptrs(const pa_push_job& job, long long r, const uint4*& s, uint4*& d) {
@@ -32,20 +34,19 @@ __device__ __forceinline__ void push_row_ptrs(const pa_push_job& job, long long 
                                  row * job.dst_stride[2]);
 }
 
-// grid = (ctas_per_dest, n_dest). A row is 128 x 16-bit = 256 B = 16 lanes x 16 B.
-__global__ void __launch_bounds__(kPushThreads, 6)
-cp_push_kernel(const __grid_constant__ PushParams p) {
-    const int dest = blockIdx.y;
+// All threads of the calling CTA copy this CTA's share (CTA `cta` of `n_ctas`) of every job
+// bound for `dest`, then one thread publishes the arrival with a system-scope release.
+// A row is 128 x 16-bit = 256 B = 16 lanes x 16 B. Must be called by the whole CTA.
+__device__ __forceinline__ void push_to_dest(const PushParams& p, int dest, int cta, int n_ctas) {
     const int lane16 = threadIdx.x & 15;
-    const int sub = threadIdx.x >> 4;                       // row slot inside the CTA
-    constexpr int rows_per_cta = kPushThreads / 16;         // rows per CTA per unroll step
-    const long long step = static_cast<long long>(gridDim.x) * rows_per_cta;
+    const int sub = threadIdx.x >> 4;
+    const int rows_per_cta = blockDim.x >> 4;
+    const long long step = static_cast<long long>(n_ctas) * rows_per_cta;
     for (int j = 0; j < p.n_jobs; ++j) {
         const pa_push_job& job = p.jobs[j];
         if (job.dest != dest) continue;
         const long long total = static_cast<long long>(job.batch) * job.heads * job.rows;
-        for (long long r0 = static_cast<long long>(blockIdx.x) * rows_per_cta + sub; r0 < total;
-             r0 += step * kPushUnroll) {
+        for (long long r0 = static_cast<long long>(cta) * rows_per_cta + sub; r0 < total; r0 += step * kPushUnroll) {
             uint4 val[kPushUnroll];
             uint4* dptr[kPushUnroll];
 #pragma unroll
@@ -68,6 +69,12 @@ cp_push_kernel(const __grid_constant__ PushParams p) {
         __threadfence_system();
         red_release_sys_add(p.flag[dest], 1u);
     }
+}
+
+// Stand-alone form: grid = (ctas_per_dest, n_dest).
+__global__ void __launch_bounds__(kPushThreads, 6)
+cp_push_kernel(const __grid_constant__ PushParams p) {
+    push_to_dest(p, blockIdx.y, blockIdx.x, gridDim.x);
 }
 
 struct FlagWaitParams {

@@ -11,7 +11,6 @@
 
 #include "../../include/pa_b200.h"
 #include "attn_fwd_sm100.cuh"
-#include "cp_exchange_sm100.cuh"
 #include "fbc_sm100.cuh"
 #include "merge_sm100.cuh"
 
@@ -78,7 +77,7 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int rows, int heads,
 
 template <bool kBF16, bool kDebug>
 int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const pa::AttnParams& p,
-                int grid, cudaStream_t stream) {
+                const pa::PushParams& push, int grid, cudaStream_t stream) {
     auto kern = pa::attn_fwd_kernel<kBF16, kDebug>;
     static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
@@ -92,7 +91,7 @@ int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
-    kern<<<grid, pa::kAttnThreads, pa::kAttnSmemBytes, stream>>>(mq, mk, mv, p);
+    kern<<<grid, pa::kAttnThreads, pa::kAttnSmemBytes, stream>>>(mq, mk, mv, p, push);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(PA_ECUDA, "attention launch: %s", cudaGetErrorString(e));
     return PA_OK;
@@ -113,7 +112,8 @@ int out_checks(const void* out, const int64_t* o_stride) {
     return PA_OK;
 }
 
-int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, int v_sbo, int pv_split, bool debug) {
+int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, int v_sbo, int pv_split, bool debug,
+                  long long* dbg_t = nullptr, int dbg_steps = 0) {
     if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
     if (!a->q || !a->k || !a->v || !a->out) return fail(PA_EINVAL, "q, k, v and out must be non-NULL");
     if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0)
@@ -154,17 +154,47 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     p.v_lbo = v_lbo;
     p.v_sbo = v_sbo;
     p.pv_split = pv_split;
+    p.dbg_t = dbg_t;
+    p.dbg_steps = dbg_steps;
 
     const long long pairs = (a->seq_q + 255) / 256;
     const long long grid = pairs * a->heads * a->batch;
     if (grid > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    pa::PushParams push;
+    memset(&push, 0, sizeof(push));
     if (debug) {
-        return a->dtype == PA_BF16 ? launch_attn<true, true>(mq, mk, mv, p, int(grid), s)
-                                   : launch_attn<false, true>(mq, mk, mv, p, int(grid), s);
+        return a->dtype == PA_BF16 ? launch_attn<true, true>(mq, mk, mv, p, push, int(grid), s)
+                                   : launch_attn<false, true>(mq, mk, mv, p, push, int(grid), s);
     }
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, int(grid), s)
-                               : launch_attn<false, false>(mq, mk, mv, p, int(grid), s);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, push, int(grid), s)
+                               : launch_attn<false, false>(mq, mk, mv, p, push, int(grid), s);
+}
+
+int fill_push(const pa_cp_push_args* a, pa::PushParams* p) {
+    if (a->n_jobs < 0 || a->n_jobs > PA_MAX_PUSH_JOBS) return fail(PA_EINVAL, "n_jobs must be in [0, %d]", PA_MAX_PUSH_JOBS);
+    if (a->n_dest < 1 || a->n_dest > PA_MAX_CHUNKS) return fail(PA_EINVAL, "n_dest must be in [1, %d]", PA_MAX_CHUNKS);
+    if (a->ctas_per_dest < 1 || a->ctas_per_dest > 1024) return fail(PA_EINVAL, "ctas_per_dest must be in [1, 1024]");
+    if (a->first_dest < 0 || a->first_dest >= a->n_dest) return fail(PA_EINVAL, "first_dest out of range");
+    memset(p, 0, sizeof(*p));
+    for (int j = 0; j < a->n_jobs; ++j) {
+        const pa_push_job& job = a->jobs[j];
+        if (!job.src || !job.dst) return fail(PA_EINVAL, "job %d: src and dst must be non-NULL", j);
+        if (job.dest < 0 || job.dest >= a->n_dest) return fail(PA_EINVAL, "job %d: dest out of range", j);
+        if (job.batch <= 0 || job.heads <= 0 || job.rows <= 0 || job.head0 < 0)
+            return fail(PA_EINVAL, "job %d: batch, heads, rows must be positive", j);
+        if ((reinterpret_cast<uintptr_t>(job.src) & 15u) || (reinterpret_cast<uintptr_t>(job.dst) & 15u))
+            return fail(PA_EINVAL, "job %d: src and dst must be 16-byte aligned", j);
+        for (int i = 0; i < 3; ++i)
+            if ((job.src_stride[i] * 2) % 16 != 0 || (job.dst_stride[i] * 2) % 16 != 0)
+                return fail(PA_EINVAL, "job %d: byte strides must be multiples of 16", j);
+        p->jobs[j] = job;
+    }
+    p->n_jobs = a->n_jobs;
+    p->n_dest = a->n_dest;
+    p->first_dest = a->first_dest;
+    for (int d = 0; d < PA_MAX_CHUNKS; ++d) p->flag[d] = a->flag[d];
+    return PA_OK;
 }
 
 }  // namespace
@@ -180,6 +210,10 @@ int pa_attn_fwd(const pa_attn_args* args, void* stream) {
 
 int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo, int pv_split, void* stream) {
     return attn_fwd_impl(args, stream, dbg_s, v_lbo, v_sbo, pv_split, true);
+}
+
+int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps, void* stream) {
+    return attn_fwd_impl(args, stream, nullptr, pa::kHalfBytes, 1024, 0, true, stamps, steps);
 }
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
@@ -240,34 +274,27 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     const long long pairs = (a->q_rows + 255) / 256;
     const long long grid = pairs * a->heads * a->batch * a->n_q_chunks;
     if (grid > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
+    pa::PushParams push;
+    memset(&push, 0, sizeof(push));
+    if (a->fused_push != nullptr) {
+        rc = fill_push(a->fused_push, &push);
+        if (rc != PA_OK) return rc;
+        // pushers must all be resident at once: never more than the grid or one wave of SMs
+        int n = a->fused_push->ctas_per_dest;
+        if (n > grid) n = int(grid);
+        if (n > 128) n = 128;
+        push.n_push_ctas = n;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, int(grid), s)
-                               : launch_attn<false, false>(mq, mk, mv, p, int(grid), s);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, push, int(grid), s)
+                               : launch_attn<false, false>(mq, mk, mv, p, push, int(grid), s);
 }
 
 int pa_cp_push(const pa_cp_push_args* a, void* stream) {
     if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
-    if (a->n_jobs < 0 || a->n_jobs > PA_MAX_PUSH_JOBS) return fail(PA_EINVAL, "n_jobs must be in [0, %d]", PA_MAX_PUSH_JOBS);
-    if (a->n_dest < 1 || a->n_dest > PA_MAX_CHUNKS) return fail(PA_EINVAL, "n_dest must be in [1, %d]", PA_MAX_CHUNKS);
-    if (a->ctas_per_dest < 1 || a->ctas_per_dest > 1024) return fail(PA_EINVAL, "ctas_per_dest must be in [1, 1024]");
     pa::PushParams p;
-    memset(&p, 0, sizeof(p));
-    for (int j = 0; j < a->n_jobs; ++j) {
-        const pa_push_job& job = a->jobs[j];
-        if (!job.src || !job.dst) return fail(PA_EINVAL, "job %d: src and dst must be non-NULL", j);
-        if (job.dest < 0 || job.dest >= a->n_dest) return fail(PA_EINVAL, "job %d: dest out of range", j);
-        if (job.batch <= 0 || job.heads <= 0 || job.rows <= 0 || job.head0 < 0)
-            return fail(PA_EINVAL, "job %d: batch, heads, rows must be positive", j);
-        if ((reinterpret_cast<uintptr_t>(job.src) & 15u) || (reinterpret_cast<uintptr_t>(job.dst) & 15u))
-            return fail(PA_EINVAL, "job %d: src and dst must be 16-byte aligned", j);
-        for (int i = 0; i < 3; ++i)
-            if ((job.src_stride[i] * 2) % 16 != 0 || (job.dst_stride[i] * 2) % 16 != 0)
-                return fail(PA_EINVAL, "job %d: byte strides must be multiples of 16", j);
-        p.jobs[j] = job;
-    }
-    p.n_jobs = a->n_jobs;
-    p.n_dest = a->n_dest;
-    for (int d = 0; d < PA_MAX_CHUNKS; ++d) p.flag[d] = a->flag[d];
+    int rc = fill_push(a, &p);
+    if (rc != PA_OK) return rc;
     dim3 grid(a->ctas_per_dest, a->n_dest);
     pa::cp_push_kernel<<<grid, pa::kPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     cudaError_t e = cudaGetLastError();

@@ -260,6 +260,40 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// 2^x for a pair of values on the FMA pipe instead of the special-function unit: round x to
+// the nearest integer n with the 1.5*2^23 trick, evaluate a cubic in f = x - n (|f| <= 0.5,
+// relative error 7.8e-5, far below the 2^-8 resolution of the bf16 probabilities), and add n
+// to the exponent field. x is clamped at -126 (result ~1e-38, i.e. zero for softmax purposes).
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 xf = __fadd2_rn(x, make_float2(12582912.0f, 12582912.0f));
+    const float2 n = __fadd2_rn(xf, make_float2(-12582912.0f, -12582912.0f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(make_float2(0.05508868f, 0.05508868f), f, make_float2(0.24260405f, 0.24260405f));
+    p = __ffma2_rn(p, f, make_float2(0.69327623f, 0.69327623f));
+    p = __ffma2_rn(p, f, make_float2(0.99992895f, 0.99992895f));
+    float2 r;
+    r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(xf.x) << 23));
+    r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(xf.y) << 23));
+    return r;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

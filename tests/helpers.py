@@ -79,6 +79,31 @@ class LocalCluster:
         self.capacity = need
         self.state = E.CallState()
 
+    def attention_fused_single_rank(self, q, k, v, scale=None, ctas=4, wait_ns=200_000_000):
+        """World size 1 only: the exchange rides inside the attention launch (the form multi-GPU
+        runs use). The pushing CTAs belong to the same launch as the CTAs that wait for them."""
+        assert self.W == 1
+        E = self.E
+        B, H, sq, D = q.shape
+        skv = k.shape[2]
+        plan = E.CpPlan(1, 1, 0, 0, H)
+        self._ensure(plan, B, sq, skv, D, q.element_size())
+        st = self.state
+        par = st.calls & 1
+        st.calls += 1
+        n_push = E.fused_push_ctas(plan, B, sq, ctas)
+        st.arrive_expect[par] += n_push
+        q, k, v = E._fix(q), E._fix(k), E._fix(v)
+        push = E.build_push_args(plan, self.ws[0], par, q, k, v, n_push)
+        out = torch.empty((B, sq, H, D), dtype=q.dtype, device=self.device).transpose(1, 2)
+        scale = (1.0 / math.sqrt(D)) if scale is None else scale
+        E.launch_attention(plan, self.ws[0], par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par], wait_ns,
+                           torch.cuda.current_stream(self.device).cuda_stream, out, push)
+        torch.cuda.synchronize(self.device)
+        code = int(self.ws[0].status_tensor().item())
+        assert code == 0, f"device status {code}"
+        return out
+
     def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000):
         E = self.E
         B, H, sq, D = qs[0].shape

@@ -86,6 +86,21 @@ def test_sharded_equals_single_device_full_size_shard():
     assert_attention_close(full[:, :, idx], ref, "sampled rows")
 
 
+@pytest.mark.parametrize("B,H,S,ctas", [(1, 2, 300, 4), (2, 3, 4095, 16), (1, 1, 100, 64)])
+def test_fused_push_inside_attention_launch(B, H, S, ctas):
+    """The form multi-GPU runs use: the leading CTAs of the attention grid do the exchange.
+    With one rank everything a CTA waits for is produced by CTAs of the same launch."""
+    q, k, v = seeded_qkv(B, H, S, S, seed=S, bshd=True)
+    cluster = LocalCluster(1, 1)
+    ref, _ = O.sdpa_with_lse(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy())
+    first = None
+    for rep in range(3):  # both staging parities and the monotonic counters
+        out = cluster.attention_fused_single_rank(q, k, v, ctas=ctas)
+        assert_attention_close(out, ref, f"fused push call {rep}")
+        first = out if first is None else first
+        assert torch.equal(out, first)
+
+
 def test_wait_runs_out_and_reports_status():
     """A chunk whose arrival counter nothing sets: the bounded wait gives up, the status word
     says which wait it was, and the context stays usable."""
