@@ -1,15 +1,19 @@
 // Flash-attention forward for B200 (sm_100a): tcgen05 MMA with TMEM accumulators, TMA loads.
 //
 // One CTA owns two query tiles of 128 rows (same batch/head/chunk) and walks every key/value
-// tile of 128 rows. Warp roles:
-//   warps 0-3  softmax for query tile 0 (one thread per row, TMEM lane = row)
-//   warps 4-7  softmax for query tile 1
-//   warp  8    MMA issuer (one thread): S_t = Q_t K_j^T into TMEM, O_t += P_t V_j from TMEM
-//   warp  9    TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
-//   warps 10-11 idle; they complete the control warpgroup that gives its registers away
+// tile of 128 rows. Warp roles (20 warps):
+//   warps 0-15  softmax. Warp w serves TMEM lane quarter w%4 (32 query rows) of query tile
+//               (w/4)%2 and key-column half w/8: two threads share a query row, each owns
+//               64 of the tile's 128 key columns (and, in the epilogue, 64 of O's columns).
+//   warp  16    MMA issuer (one thread): S_t = Q_t K_j^T into TMEM, O_t += P_t V_j from TMEM
+//   warp  17    TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
+//   warps 18-19 idle; they complete the control warpgroup that gives registers away
 // TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512);
-// P_t (bf16/f16, 64 columns) overwrites the front of S_t and is the TMEM A operand of P V.
-// While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs.
+// P_t (bf16/f16) overwrites S_t in place - each thread packs its 64 probabilities into the
+// first 32 of its own 64 logit columns - and is the TMEM A operand of P V.
+// While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs; the
+// two column halves of P are handed over separately, so P V starts on the first half while the
+// second is still being exponentiated.
 //
 // In context-parallel runs the same launch also performs the exchange (see the fused push
 // below): one kernel per attention call and rank, no collective library call on the path.
@@ -36,30 +40,24 @@ constexpr int kTileN = 128;
 constexpr int kHalfBytes = 128 * 128;       // 128 rows x 64 elements x 2 B (one swizzle atom wide)
 constexpr int kTileBytes = 2 * kHalfBytes;  // 128 x 128 x 2 B
 constexpr int kStages = 2;
-constexpr int kSoftmaxWarps = 8;
-constexpr int kMmaWarp = 8;
-constexpr int kTmaWarp = 9;
-constexpr int kAttnThreads = 384;  // 2 softmax warpgroups + 1 control warpgroup (MMA, TMA, 2 idle warps)
+constexpr int kSoftmaxWarps = 16;
+constexpr int kMmaWarp = 16;
+constexpr int kTmaWarp = 17;
+constexpr int kAttnThreads = 640;  // 4 softmax warpgroups + 1 control warpgroup
 #ifndef PA_REGS_SOFTMAX
-#define PA_REGS_SOFTMAX 200
+#define PA_REGS_SOFTMAX 104
 #endif
 #ifndef PA_REGS_CONTROL
-#define PA_REGS_CONTROL 104
+#define PA_REGS_CONTROL 64
 #endif
+constexpr int kRegsLaunch = 96;  // 65536 / 640 rounded down to a multiple of 8
 constexpr int kRegsSoftmax = PA_REGS_SOFTMAX;
 constexpr int kRegsControl = PA_REGS_CONTROL;
-// The CTA is launched with 168 registers per thread (the cap for 384 threads). Each scheduler
-// partition holds one warp of each warpgroup, so what the two softmax warps gain must be
-// covered by what the control warp gives up - otherwise setmaxnreg.inc would wait forever.
-static_assert(2 * kRegsSoftmax + kRegsControl <= 3 * 168, "setmaxnreg budget exceeds the launch allocation");
+// Each scheduler partition holds one warp of each of the five warpgroups, so what its four
+// softmax warps gain must be covered by what its control warp gives up - otherwise
+// setmaxnreg.inc would wait forever.
+static_assert(4 * kRegsSoftmax + kRegsControl <= 5 * kRegsLaunch, "setmaxnreg budget exceeds the launch allocation");
 static_assert(kRegsSoftmax % 8 == 0 && kRegsControl % 8 == 0, "setmaxnreg counts are multiples of 8");
-// The MMA issuer must keep ahead of the tensor core (64 cycles per 128x128x16 MMA): its k-step
-// loops are unrolled so that an issue costs a handful of instructions.
-#if defined(PA_ROLLED_MMA) && PA_ROLLED_MMA
-#define PA_MMA_UNROLL _Pragma("unroll 1")
-#else
-#define PA_MMA_UNROLL _Pragma("unroll")
-#endif
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColO0 = 256;
 // log2-domain growth of the running row maximum that is tolerated before O is rescaled
@@ -69,6 +67,10 @@ constexpr float kRescaleThreshold = 8.0f;
 #define PA_POLY_PAIRS_OF_8 0
 #endif
 constexpr int kPolyPairsOf8 = PA_POLY_PAIRS_OF_8;
+#ifndef PA_POLY_HALF1
+#define PA_POLY_HALF1 0
+#endif
+constexpr bool kPolyHalf1 = PA_POLY_HALF1 != 0;
 
 struct AttnParams {
     int batch, heads;
@@ -93,9 +95,12 @@ struct AttnParams {
     int dbg_steps;
 };
 
+#ifndef PA_TIMELINE
+#define PA_TIMELINE 0  // 1: the stamps are also compiled into the production instantiation (profiling builds)
+#endif
 template <bool kDebug>
 __device__ __forceinline__ void dbg_stamp(const AttnParams& p, int role, int step, int slot, bool who) {
-    if (kDebug) {
+    if (kDebug || PA_TIMELINE) {
         if (p.dbg_t != nullptr && blockIdx.x == 0 && who && step < p.dbg_steps)
             p.dbg_t[(static_cast<size_t>(role) * p.dbg_steps + step) * 8 + slot] = clock64();
     }
@@ -105,16 +110,22 @@ struct AttnSmemCtl {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages];
     uint64_t v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2], p_full[2], o_done[2];
+    uint64_t s_full[2], p_full[2][2], o_done[2];
     uint64_t teardown;
     uint32_t tmem_base;
     int abort;
+    float xch[2][2][2][kTileM];  // [step parity][query tile][column half][row]: row max / row sum exchange
 };
 
+constexpr int kAttnCtlBytes = 4608;
 constexpr int kAttnSmemBytes = 1024 /*align slack*/ + 2 * kTileBytes /*Q*/ +
-                               kStages * kTileBytes /*K*/ + kStages * kTileBytes /*V*/ +
-                               256 /*control*/;
-static_assert(sizeof(AttnSmemCtl) <= 256, "control block too large");
+                               kStages * kTileBytes /*K*/ + kStages * kTileBytes /*V*/ + kAttnCtlBytes;
+static_assert(sizeof(AttnSmemCtl) <= kAttnCtlBytes, "control block too large");
+
+// Barrier among the 64 threads (two warps) that share 32 query rows.
+__device__ __forceinline__ void pair_sync(int id) {
+    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
 
 template <bool kBF16, bool kDebug>
 __global__ void __launch_bounds__(kAttnThreads, 1)
@@ -152,7 +163,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(smem_u32(&ctl->s_full[t]), 1);
-            mbar_init(smem_u32(&ctl->p_full[t]), 128);
+            mbar_init(smem_u32(&ctl->p_full[t][0]), 128);
+            mbar_init(smem_u32(&ctl->p_full[t][1]), 128);
             mbar_init(smem_u32(&ctl->o_done[t]), 1);
         }
         mbar_init(smem_u32(&ctl->teardown), 1);
@@ -201,10 +213,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     }
 
-    // Registers move from the control warpgroup to the softmax warpgroups (per scheduler
-    // partition: 2 x 200 + 112 registers x 32 lanes fill the 16K file).
-    // (each role's code is dominated by its own setmaxnreg so that the register allocator
-    // budgets the three regions separately)
+    // Registers move from the control warpgroup to the softmax warpgroups. Each role's code is
+    // dominated by its own setmaxnreg so that the register allocator budgets the regions
+    // separately.
     if (warp >= kSoftmaxWarps) setmaxnreg_dec<kRegsControl>();
     if (warp == kTmaWarp) {
         // =============================== TMA producer ======================================
@@ -280,6 +291,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     } else if (warp == kMmaWarp) {
         // =============================== MMA issuer ========================================
+        // The issuer must keep ahead of the tensor core (64 cycles per 128x128x16 MMA): the
+        // k-step loops are unrolled and every descriptor is a base plus a constant.
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN);
             constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kHeadDim);
@@ -297,25 +310,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const uint64_t a0 = dq0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
                 const uint64_t b0 = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
                 const uint32_t d = tmem + kColS0 + t * kTileN;
-                PA_MMA_UNROLL
+#pragma unroll
                 for (int ks = 0; ks < kHeadDim / 16; ++ks) {
                     const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
                     tc_mma_ss(d, a0 + off, b0 + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int t, int st, bool acc) {
+            // P V for key rows [64*half, 64*half+64) of the tile: four k-steps
+            auto issue_pv_half = [&](int t, int st, int half, bool acc) {
                 const uint64_t b0 = dv0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
                 const uint32_t a0 = tmem + kColS0 + t * kTileN;
                 const uint32_t d = tmem + kColO0 + t * kHeadDim;
-                PA_MMA_UNROLL
-                for (int ks = 0; ks < kTileN / 16; ++ks) {
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const int ks = half * 4 + k4;
                     const uint64_t b = b0 + static_cast<uint64_t>((ks * 16 * 128) >> 4);
                     const uint32_t accum = (acc || ks > 0) ? 1u : 0u;
+                    // P of column half h lives at S columns [64h, 64h+32): 8 columns per k-step
+                    const uint32_t a = a0 + half * 64 + k4 * 8;
                     if (!pv_split) {
-                        tc_mma_ts(d, a0 + ks * 8, b, idesc_pv, accum);
+                        tc_mma_ts(d, a, b, idesc_pv, accum);
                     } else {
-                        tc_mma_ts(d, a0 + ks * 8, b, idesc_pv64, accum);
-                        tc_mma_ts(d + 64, a0 + ks * 8, b + static_cast<uint64_t>(kHalfBytes >> 4), idesc_pv64, accum);
+                        tc_mma_ts(d, a, b, idesc_pv64, accum);
+                        tc_mma_ts(d + 64, a, b + static_cast<uint64_t>(kHalfBytes >> 4), idesc_pv64, accum);
                     }
                 }
             };
@@ -347,12 +364,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
                     dbg_stamp<kDebug>(p, 2, j, t * 4 + 0, true);
-                    ok = mbar_wait(smem_u32(&ctl->p_full[t]), j & 1, s_abort, p.status, pipe_limit,
+                    ok = mbar_wait(smem_u32(&ctl->p_full[t][0]), j & 1, s_abort, p.status, pipe_limit,
                                    PA_DEV_TIMEOUT_PIPE);
                     if (!ok) break;
                     dbg_stamp<kDebug>(p, 2, j, t * 4 + 1, true);
                     tc_fence_after();
-                    issue_pv(t, st, j > 0);
+                    issue_pv_half(t, st, 0, j > 0);
+                    ok = mbar_wait(smem_u32(&ctl->p_full[t][1]), j & 1, s_abort, p.status, pipe_limit,
+                                   PA_DEV_TIMEOUT_PIPE);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv_half(t, st, 1, j > 0);
                     tc_commit(smem_u32(&ctl->o_done[t]));
                     if (t == 1) tc_commit(smem_u32(&ctl->v_empty[st]));
                     dbg_stamp<kDebug>(p, 2, j, t * 4 + 2, true);
@@ -375,72 +397,83 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     } else if (warp < kSoftmaxWarps) {
         // =============================== softmax + epilogue ================================
         setmaxnreg_inc<kRegsSoftmax>();
-        const int t = warp >> 2;
         const int quarter = warp & 3;
+        const int t = (warp >> 2) & 1;
+        const int half = warp >> 3;
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN;
-        const uint32_t tO = tmem + lane_base + kColO0 + t * kHeadDim;
+        const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN + half * 64;  // my 64 logit columns
+        const uint32_t tO = tmem + lane_base + kColO0 + t * kHeadDim + half * 64;  // my 64 output columns
         const uint32_t bs = smem_u32(&ctl->s_full[t]);
-        const uint32_t bp = smem_u32(&ctl->p_full[t]);
+        const uint32_t bp = smem_u32(&ctl->p_full[t][half]);
         const uint32_t bo = smem_u32(&ctl->o_done[t]);
+        const int pair_bar = 1 + t * 4 + quarter;
         const float sl = p.scale_log2;
+        const bool stamper = (quarter == 0 && lane == 0 && half == 0);
 
         float m_ref = -INFINITY;
-        float l_sum = 0.f;
+        float l_sum = 0.f;  // over my columns only
         bool ok = true;
         int j = 0;
-        for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
+        for (int ci = 0; ci < p.n_kv_chunks; ++ci) {
             for (int tk = 0; tk < tiles_per_chunk; ++tk, ++j) {
-                const int valid = min(kTileN, p.kv_rows - tk * kTileN);
-                const bool stamper = (quarter == 0 && lane == 0);
+                const int valid = min(kTileN, p.kv_rows - tk * kTileN) - half * 64;  // of my 64 columns
                 dbg_stamp<kDebug>(p, t, j, 0, stamper);
-                ok = mbar_wait(bs, j & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE);
-                if (!ok) break;
+                // A wait that gives up does not leave the loop: the two partner warps must meet at
+                // every pair barrier below, and once the abort word is set no wait blocks any more.
+                ok = mbar_wait(bs, j & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
                 dbg_stamp<kDebug>(p, t, j, 1, stamper);
                 tc_fence_after();
-                uint32_t s[4][32];
+                // Pass 1: row maximum of my 64 logits. The logits are not kept: pass 2 reads them
+                // again from TMEM 32 columns at a time, which keeps the thread within its register
+                // budget (TMEM bandwidth is plentiful, registers are not).
+                float mx[2];
+                {
+                    uint32_t s[2][32];
+                    tmem_ld32(tS, s[0]);
+                    tmem_ld32(tS + 32, s[1]);
+                    tc_wait_ld();
+                    tmem_ld_fence(s[0]);
+                    tmem_ld_fence(s[1]);
+                    dbg_stamp<kDebug>(p, t, j, 2, stamper);
+                    if (kDebug && p.dbg_s != nullptr && blockIdx.x == 0) {
+                        float* d = p.dbg_s + ((static_cast<size_t>(t) * n_tiles + j) * 128 + row_in_tile) * 128 + half * 64;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, s[c]);
-                tc_wait_ld();
+                        for (int c = 0; c < 2; ++c)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld_fence(s[c]);
-                dbg_stamp<kDebug>(p, t, j, 2, stamper);
-                if (kDebug && p.dbg_s != nullptr && blockIdx.x == 0) {
-                    float* d = p.dbg_s + ((static_cast<size_t>(t) * n_tiles + j) * 128 + row_in_tile) * 128;
+                            for (int i = 0; i < 32; ++i) d[c * 32 + i] = __uint_as_float(s[c][i]);
+                    }
+                    if (valid < 64) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
+                        for (int c = 0; c < 2; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) d[c * 32 + i] = __uint_as_float(s[c][i]);
+                            for (int i = 0; i < 32; ++i)
+                                if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
+                    }
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        mx[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
+#pragma unroll
+                        for (int i = 2; i < 32; i += 2)
+                            mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+                    }
                 }
-                if (valid < kTileN) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
-                }
-                float mx[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    mx[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
-#pragma unroll
-                    for (int i = 2; i < 32; i += 2)
-                        mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
-                }
-                const float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), m_ref);
+                // row maximum over both column halves: swap partial maxima with the partner thread
+                const float mine = fmaxf(mx[0], mx[1]);
+                ctl->xch[j & 1][t][half][row_in_tile] = mine;
+                pair_sync(pair_bar);
+                const float m_new = fmax3(mine, ctl->xch[j & 1][t][half ^ 1][row_in_tile], m_ref);
                 const bool grow = (m_new - m_ref) * sl > kRescaleThreshold;
-                if (__any_sync(0xffffffffu, grow)) {
+                if (__any_sync(0xffffffffu, grow)) {  // same decision in both partner warps
                     const float alpha = ex2_approx((m_ref - m_new) * sl);
                     l_sum *= alpha;
                     m_ref = m_new;
                     if (j > 0) {
                         ok = mbar_wait(bo, (j - 1) & 1, s_abort, p.status, pipe_limit,
-                                       PA_DEV_TIMEOUT_PIPE);
-                        if (!ok) break;
+                                       PA_DEV_TIMEOUT_PIPE) && ok;
                         tc_fence_after();
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
+                        for (int c = 0; c < 2; ++c) {
                             uint32_t o[32];
                             tmem_ld32(tO + c * 32, o);
                             tc_wait_ld();
@@ -450,42 +483,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                 o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
                             tmem_st32(tO + c * 32, o);
                         }
+                        // P V of this step adds to all 128 output columns as soon as the first
+                        // half of P is handed over: both halves of O must be rescaled by then.
+                        tc_wait_st();
+                        tc_fence_before();
+                        pair_sync(pair_bar);
+                        tc_fence_after();
                     }
                 }
                 const float neg = -m_ref * sl;
                 dbg_stamp<kDebug>(p, t, j, 3, stamper);
-                // p = 2^(s*sl - m*sl): packed fp32x2 arithmetic; kPolyPairsOf8 of every 8 element
-                // pairs take the FMA-pipe polynomial, the rest the special-function unit, so that
-                // neither pipe alone bounds the softmax.
+                // p = 2^(s*sl - m*sl) in packed fp32x2 arithmetic. The exponentials are split between
+                // the special-function unit and an FMA-pipe polynomial so that neither pipe alone
+                // bounds the softmax: either the warps of column half 1 take the polynomial for all
+                // their elements (kPolyHalf1) or kPolyPairsOf8 of every 8 element pairs do.
                 const float2 sl2 = make_float2(sl, sl);
                 const float2 neg2 = make_float2(neg, neg);
-                float2 ls[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f),
-                                make_float2(0.f, 0.f)};
+                // Pass 2, per 32-column chunk: reload, exponentiate, pack, and store the 16 packed
+                // words over logit columns of my own that are already consumed (chunk c goes to my
+                // columns [16c, 16c+16)), so partner threads never touch each other's columns.
+                float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t pk[32];
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t sc[32];
+                    tmem_ld32(tS + c * 32, sc);
+                    tc_wait_ld();
+                    tmem_ld_fence(sc);
+                    if (valid < 64) {
 #pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) {
-                        const int c = half * 2 + cc;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float2 x = __ffma2_rn(
-                                make_float2(__uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1])), sl2, neg2);
-                            float2 e;
-                            if (((i >> 1) & 7) < kPolyPairsOf8) {
-                                e = exp2_poly2(x);
-                            } else {
-                                e.x = ex2_approx(x.x);
-                                e.y = ex2_approx(x.y);
-                            }
-                            ls[c] = __fadd2_rn(ls[c], e);
-                            pk[cc * 16 + (i >> 1)] = kBF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
-                        }
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= valid) sc[i] = 0xff800000u;  // -inf
                     }
-                    tmem_st32(tS + half * 32, pk);
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float2 x = __ffma2_rn(
+                            make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), sl2, neg2);
+                        float2 e;
+                        if (kPolyHalf1 ? (half == 1) : (((i >> 1) & 7) < kPolyPairsOf8)) {
+                            e = exp2_poly2(x);
+                        } else {
+                            e.x = ex2_approx(x.x);
+                            e.y = ex2_approx(x.y);
+                        }
+                        ls[c] = __fadd2_rn(ls[c], e);
+                        pk[i >> 1] = kBF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
+                    }
+                    tmem_st16(tS + c * 16, pk);
                 }
                 {
-                    const float2 a = __fadd2_rn(__fadd2_rn(ls[0], ls[1]), __fadd2_rn(ls[2], ls[3]));
+                    const float2 a = __fadd2_rn(ls[0], ls[1]);
                     l_sum += a.x + a.y;
                 }
                 dbg_stamp<kDebug>(p, t, j, 4, stamper);
@@ -495,17 +542,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 dbg_stamp<kDebug>(p, t, j, 5, stamper);
             }
         }
-        if (ok) ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE);
+        ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
+        // row sum over both halves
+        ctl->xch[n_tiles & 1][t][half][row_in_tile] = l_sum;
+        pair_sync(pair_bar);
+        const float l_row = l_sum + ctl->xch[n_tiles & 1][t][half ^ 1][row_in_tile];
         if (ok) {
             tc_fence_after();
             const int row = row0 + t * kTileM + row_in_tile;
             const bool in_range = row < p.q_rows;
-            const float inv = 1.0f / l_sum;
+            const float inv = 1.0f / l_row;
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
                              (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
-                              static_cast<long long>(row) * p.o_ss);
+                              static_cast<long long>(row) * p.o_ss) + half * 64;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t o[32];
                 tmem_ld32(tO + c * 32, o);
                 tc_wait_ld();
@@ -525,9 +576,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     }
                 }
             }
-            if (in_range && p.lse[qc] != nullptr) {
+            if (half == 0 && in_range && p.lse[qc] != nullptr) {
                 p.lse[qc][static_cast<long long>(bidx) * p.l_sb + static_cast<long long>(head) * p.l_sh + row] =
-                    m_ref * p.scale + __logf(l_sum);
+                    m_ref * p.scale + __logf(l_row);
             }
         }
     }

@@ -213,7 +213,7 @@ int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo
 }
 
 int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps, void* stream) {
-    return attn_fwd_impl(args, stream, nullptr, pa::kHalfBytes, 1024, 0, true, stamps, steps);
+    return attn_fwd_impl(args, stream, nullptr, pa::kHalfBytes, 1024, 0, PA_TIMELINE ? false : true, stamps, steps);
 }
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
