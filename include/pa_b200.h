@@ -119,6 +119,18 @@ typedef struct pa_cp_attn_args {
      * flag_expect must therefore grow by that CTA count per call. The host struct is read
      * during the call only. */
     const struct pa_cp_push_args* fused_push;
+    /* Zero-copy own shard (each may be NULL): when given, query chunk q_first (key/value chunk
+     * kv_first) is not read from the staging buffer but straight from this rank's own tensor,
+     * [batch, all heads, rows, 128] with the given element strides, heads
+     * [local_head_offset, local_head_offset + heads); its ready flag is ignored. */
+    const void* q_local;
+    const void* k_local;
+    const void* v_local;
+    int64_t q_local_stride[3];
+    int64_t k_local_stride[3];
+    int64_t v_local_stride[3];
+    int32_t local_head_offset;
+    int32_t local_total_heads;
 } pa_cp_attn_args;
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);

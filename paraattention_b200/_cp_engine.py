@@ -81,12 +81,16 @@ class CpPlan:
     def flat(self, u: int, r: int) -> int:
         return r * self.ulysses + u
 
-    def push_jobs(self) -> List[PushJobSpec]:
+    def push_jobs(self, skip_self: bool = False) -> List[PushJobSpec]:
+        """Copies this rank owes to every rank. With ``skip_self`` the copies into its own
+        staging buffer are left out (the kernel then reads the own shard in place)."""
         hl = self.local_heads
         jobs = []
         for r_d in range(self.ring):
             for u_d in range(self.ulysses):
                 dest = self.flat(u_d, r_d)
+                if skip_self and dest == self.rank:
+                    continue
                 # K and V of my shard go to every rank; chunk slot = my flat rank
                 jobs.append(PushJobSpec("k", dest, u_d * hl, hl, self.rank))
                 jobs.append(PushJobSpec("v", dest, u_d * hl, hl, self.rank))
@@ -189,8 +193,10 @@ def launch_push(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int, strea
     L.check(L.load().pa_cp_push(C.byref(pa), stream))
 
 
-def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int) -> "L.CpPushArgs":
-    """Describe the pushes of this rank: which head-slice of q/k/v goes to which rank's buffer."""
+def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int,
+                    skip_self: bool = True) -> "L.CpPushArgs":
+    """Describe the pushes of this rank: which head-slice of q/k/v goes to which rank's buffer.
+    By default nothing is copied into the own buffer: the kernel reads the own shard in place."""
     lay = ws.layout
     B, H, sq, D = q.shape
     skv = k.shape[2]
@@ -201,7 +207,7 @@ def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int) -
     chunk_bytes = {"q": B * hl * sq * D * esz, "k": B * hl * skv * D * esz, "v": B * hl * skv * D * esz}
     stage_off = {"q": lay.off_q[par], "k": lay.off_k[par], "v": lay.off_v[par]}
     pa = L.CpPushArgs()
-    jobs = plan.push_jobs()
+    jobs = plan.push_jobs(skip_self=skip_self)
     assert len(jobs) <= L.PA_MAX_PUSH_JOBS
     for i, js in enumerate(jobs):
         t = src[js.tensor]
@@ -217,6 +223,8 @@ def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int) -
     pa.n_jobs = len(jobs)
     pa.n_dest = plan.world
     for d in range(plan.world):
+        if skip_self and d == plan.rank:
+            continue  # nothing goes to my own buffer, nobody waits for that counter
         # counter slot on the destination = my plan rank (= chunk slot of my K/V there)
         pa.flag[d] = ws.peer[d] + lay.off_arrive[par] + 4 * plan.rank
     pa.ctas_per_dest = ctas
@@ -232,10 +240,11 @@ def fused_push_ctas(plan: CpPlan, B: int, sq: int, ctas: int) -> int:
 
 def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
                      arrive_expect: int, wait_ns: int, stream: int, out_local: Optional[torch.Tensor],
-                     push: Optional["L.CpPushArgs"] = None) -> None:
+                     push: Optional["L.CpPushArgs"] = None, local_qkv=None) -> None:
     """pa_cp_attn_fwd for this rank. ``out_local`` (ring-only meshes) receives the result in
     place; otherwise tiles go to the owners' output staging buffers. With ``push`` the launch
-    also performs this rank's part of the exchange (fused form)."""
+    also performs this rank's part of the exchange (fused form). ``local_qkv`` = this rank's own
+    (q, k, v): its chunk is then read in place instead of from the staging buffer."""
     lay = ws.layout
     B, H, sq, D = shape
     hl = plan.local_heads
@@ -267,6 +276,13 @@ def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.
     a.status = base + lay.off_status
     a.wait_limit_ns = wait_ns
     a.fused_push = C.addressof(push) if push is not None else None
+    if local_qkv is not None:
+        ql, kl, vl = local_qkv
+        a.q_local, a.k_local, a.v_local = ql.data_ptr(), kl.data_ptr(), vl.data_ptr()
+        for d in range(3):
+            a.q_local_stride[d], a.k_local_stride[d], a.v_local_stride[d] = ql.stride(d), kl.stride(d), vl.stride(d)
+        a.local_head_offset = plan.u * hl
+        a.local_total_heads = H
     L.check(L.load().pa_cp_attn_fwd(C.byref(a), stream))
 
 
@@ -363,7 +379,7 @@ class CpEngine:
         if self.ulysses == 1:
             out_local = torch.empty((B, sq, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
         launch_attention(plan, ws, par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par], wait_ns,
-                         main.cuda_stream, out_local, push)
+                         main.cuda_stream, out_local, push, (q, k, v))
         if out_local is not None:
             return out_local
 

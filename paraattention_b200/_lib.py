@@ -56,6 +56,9 @@ class CpAttnArgs(C.Structure):
         ("done_flag", C.c_void_p * PA_MAX_CHUNKS),
         ("status", C.c_void_p), ("wait_limit_ns", C.c_uint64),
         ("fused_push", C.c_void_p),
+        ("q_local", C.c_void_p), ("k_local", C.c_void_p), ("v_local", C.c_void_p),
+        ("q_local_stride", C.c_int64 * 3), ("k_local_stride", C.c_int64 * 3), ("v_local_stride", C.c_int64 * 3),
+        ("local_head_offset", C.c_int32), ("local_total_heads", C.c_int32),
     ]
 
 

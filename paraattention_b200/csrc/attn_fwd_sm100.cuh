@@ -87,6 +87,8 @@ struct AttnParams {
     uint32_t* done_flag[PA_MAX_CHUNKS];
     int* status;
     unsigned long long wait_ns;
+    // chunks read in place from this rank's own tensors instead of the staging buffers (-1: none)
+    int q_local_chunk, kv_local_chunk, local_head0;
     // debug instantiation only
     float* dbg_s;      // raw S of CTA 0: [tile][kv tile][row][col]
     int v_lbo, v_sbo;  // B descriptor of V (bytes)
@@ -130,8 +132,9 @@ __device__ __forceinline__ void pair_sync(int id) {
 template <bool kBF16, bool kDebug>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ AttnParams p,
-                const __grid_constant__ PushParams push) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ql,
+                const __grid_constant__ CUtensorMap tm_kl, const __grid_constant__ CUtensorMap tm_vl,
+                const __grid_constant__ AttnParams p, const __grid_constant__ PushParams push) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -178,6 +181,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
+        if (p.q_local_chunk >= 0) tma_prefetch_desc(&tm_ql);
+        if (p.kv_local_chunk >= 0) {
+            tma_prefetch_desc(&tm_kl);
+            tma_prefetch_desc(&tm_vl);
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -222,31 +230,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            if (p.q_flag[qc] != nullptr) {
+            const bool q_in_place = (qc == p.q_local_chunk);
+            if (!q_in_place && p.q_flag[qc] != nullptr) {
                 ok = flag_wait_ge(p.q_flag[qc], p.flag_expect, s_abort, p.status, p.wait_ns,
                                   PA_DEV_TIMEOUT_Q);
                 fence_proxy_async_global();
             }
             if (ok) {
                 const uint32_t bq = smem_u32(&ctl->q_full);
+                const CUtensorMap* mq = q_in_place ? &tm_ql : &tm_q;
+                const int hq = q_in_place ? head + p.local_head0 : head;
+                const int cq = q_in_place ? 0 : qc;
                 mbar_expect_tx(bq, 2 * kTileBytes);
 #pragma unroll
                 for (int t = 0; t < 2; ++t)
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
-                        tma_load_5d(sQ + t * kTileBytes + h * kHalfBytes, &tm_q, bq, h * 64,
-                                    row0 + t * kTileM, head, bidx, qc);
+                        tma_load_5d(sQ + t * kTileBytes + h * kHalfBytes, mq, bq, h * 64,
+                                    row0 + t * kTileM, hq, bidx, cq);
             }
             int j = 0;
             for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
                 int c = p.kv_first + ci;
                 if (c >= p.n_kv_chunks) c -= p.n_kv_chunks;
-                if (p.kv_flag[c] != nullptr) {
+                const bool kv_in_place = (c == p.kv_local_chunk);
+                if (!kv_in_place && p.kv_flag[c] != nullptr) {
                     ok = flag_wait_ge(p.kv_flag[c], p.flag_expect, s_abort, p.status, p.wait_ns,
                                       PA_DEV_TIMEOUT_KV);
                     fence_proxy_async_global();
                     if (!ok) break;
                 }
+                const CUtensorMap* mk = kv_in_place ? &tm_kl : &tm_k;
+                const CUtensorMap* mv = kv_in_place ? &tm_vl : &tm_v;
+                const int hk = kv_in_place ? head + p.local_head0 : head;
+                const int ck = kv_in_place ? 0 : c;
                 for (int t = 0; t < tiles_per_chunk; ++t, ++j) {
                     const int st = j & 1;
                     const uint32_t ph = (j >> 1) & 1;
@@ -258,9 +275,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         if (!ok) break;
                     }
                     mbar_expect_tx(bk, kTileBytes);
-                    tma_load_5d(sK + st * kTileBytes, &tm_k, bk, 0, t * kTileN, head, bidx, c);
-                    tma_load_5d(sK + st * kTileBytes + kHalfBytes, &tm_k, bk, 64, t * kTileN, head,
-                                bidx, c);
+                    tma_load_5d(sK + st * kTileBytes, mk, bk, 0, t * kTileN, hk, bidx, ck);
+                    tma_load_5d(sK + st * kTileBytes + kHalfBytes, mk, bk, 64, t * kTileN, hk, bidx, ck);
                     if (j >= kStages) {
                         ok = mbar_wait(smem_u32(&ctl->v_empty[st]), ph ^ 1, s_abort, p.status,
                                        pipe_limit, PA_DEV_TIMEOUT_PIPE);
@@ -270,9 +286,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         }
                     }
                     mbar_expect_tx(bv, kTileBytes);
-                    tma_load_5d(sV + st * kTileBytes, &tm_v, bv, 0, t * kTileN, head, bidx, c);
-                    tma_load_5d(sV + st * kTileBytes + kHalfBytes, &tm_v, bv, 64, t * kTileN, head,
-                                bidx, c);
+                    tma_load_5d(sV + st * kTileBytes, mv, bv, 0, t * kTileN, hk, bidx, ck);
+                    tma_load_5d(sV + st * kTileBytes + kHalfBytes, mv, bv, 64, t * kTileN, hk, bidx, ck);
                     issued = j + 1;
                 }
             }

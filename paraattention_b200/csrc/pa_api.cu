@@ -76,8 +76,8 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int rows, int heads,
 }
 
 template <bool kBF16, bool kDebug>
-int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const pa::AttnParams& p,
-                const pa::PushParams& push, int grid, cudaStream_t stream) {
+int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
+                cudaStream_t stream) {
     auto kern = pa::attn_fwd_kernel<kBF16, kDebug>;
     static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
@@ -91,7 +91,7 @@ int launch_attn(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
             if (dev >= 0 && dev < 64) configured[dev] = true;
         }
     }
-    kern<<<grid, pa::kAttnThreads, pa::kAttnSmemBytes, stream>>>(mq, mk, mv, p, push);
+    kern<<<grid, pa::kAttnThreads, pa::kAttnSmemBytes, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p, push);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(PA_ECUDA, "attention launch: %s", cudaGetErrorString(e));
     return PA_OK;
@@ -123,7 +123,8 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     rc = out_checks(a->out, a->o_stride);
     if (rc != PA_OK) return rc;
 
-    CUtensorMap mq, mk, mv;
+    CUtensorMap maps[6];
+    CUtensorMap &mq = maps[0], &mk = maps[1], &mv = maps[2];
     rc = make_map(&mq, a->q, a->dtype, a->seq_q, a->heads, a->batch, 1, a->q_stride[2], a->q_stride[1], a->q_stride[0], 0, "q");
     if (rc != PA_OK) return rc;
     rc = make_map(&mk, a->k, a->dtype, a->seq_kv, a->heads, a->batch, 1, a->k_stride[2], a->k_stride[1], a->k_stride[0], 0, "k");
@@ -131,8 +132,13 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     rc = make_map(&mv, a->v, a->dtype, a->seq_kv, a->heads, a->batch, 1, a->v_stride[2], a->v_stride[1], a->v_stride[0], 0, "v");
     if (rc != PA_OK) return rc;
 
+    maps[3] = mq;
+    maps[4] = mk;
+    maps[5] = mv;
     pa::AttnParams p;
     memset(&p, 0, sizeof(p));
+    p.q_local_chunk = -1;
+    p.kv_local_chunk = -1;
     p.batch = a->batch;
     p.heads = a->heads;
     p.n_q_chunks = 1;
@@ -164,11 +170,11 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     pa::PushParams push;
     memset(&push, 0, sizeof(push));
     if (debug) {
-        return a->dtype == PA_BF16 ? launch_attn<true, true>(mq, mk, mv, p, push, int(grid), s)
-                                   : launch_attn<false, true>(mq, mk, mv, p, push, int(grid), s);
+        return a->dtype == PA_BF16 ? launch_attn<true, true>(maps, p, push, int(grid), s)
+                                   : launch_attn<false, true>(maps, p, push, int(grid), s);
     }
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, push, int(grid), s)
-                               : launch_attn<false, false>(mq, mk, mv, p, push, int(grid), s);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s)
+                               : launch_attn<false, false>(maps, p, push, int(grid), s);
 }
 
 int fill_push(const pa_cp_push_args* a, pa::PushParams* p) {
@@ -232,7 +238,8 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         rc = out_checks(a->out[c], a->o_stride);
         if (rc != PA_OK) return rc;
     }
-    CUtensorMap mq, mk, mv;
+    CUtensorMap maps[6];
+    CUtensorMap &mq = maps[0], &mk = maps[1], &mv = maps[2];
     const int64_t qs_h = int64_t(a->q_rows) * 128, qs_b = qs_h * a->heads, qs_c = qs_b * a->batch;
     const int64_t ks_h = int64_t(a->kv_rows) * 128, ks_b = ks_h * a->heads, ks_c = ks_b * a->batch;
     rc = make_map(&mq, a->q_stage, a->dtype, a->q_rows, a->heads, a->batch, a->n_q_chunks, 128, qs_h, qs_b, qs_c, "q_stage");
@@ -242,8 +249,34 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     rc = make_map(&mv, a->v_stage, a->dtype, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, 128, ks_h, ks_b, ks_c, "v_stage");
     if (rc != PA_OK) return rc;
 
+    maps[3] = mq;
+    maps[4] = mk;
+    maps[5] = mv;
     pa::AttnParams p;
     memset(&p, 0, sizeof(p));
+    p.q_local_chunk = -1;
+    p.kv_local_chunk = -1;
+    if (a->q_local != nullptr || a->k_local != nullptr || a->v_local != nullptr) {
+        if (a->local_head_offset < 0 || a->local_total_heads < a->local_head_offset + a->heads)
+            return fail(PA_EINVAL, "local_head_offset + heads exceeds local_total_heads");
+        p.local_head0 = a->local_head_offset;
+    }
+    if (a->q_local != nullptr) {
+        rc = make_map(&maps[3], a->q_local, a->dtype, a->q_rows, a->local_total_heads, a->batch, 1, a->q_local_stride[2],
+                      a->q_local_stride[1], a->q_local_stride[0], 0, "q_local");
+        if (rc != PA_OK) return rc;
+        p.q_local_chunk = a->q_first;
+    }
+    if (a->k_local != nullptr || a->v_local != nullptr) {
+        if (a->k_local == nullptr || a->v_local == nullptr) return fail(PA_EINVAL, "k_local and v_local go together");
+        rc = make_map(&maps[4], a->k_local, a->dtype, a->kv_rows, a->local_total_heads, a->batch, 1, a->k_local_stride[2],
+                      a->k_local_stride[1], a->k_local_stride[0], 0, "k_local");
+        if (rc != PA_OK) return rc;
+        rc = make_map(&maps[5], a->v_local, a->dtype, a->kv_rows, a->local_total_heads, a->batch, 1, a->v_local_stride[2],
+                      a->v_local_stride[1], a->v_local_stride[0], 0, "v_local");
+        if (rc != PA_OK) return rc;
+        p.kv_local_chunk = a->kv_first;
+    }
     p.batch = a->batch;
     p.heads = a->heads;
     p.n_q_chunks = a->n_q_chunks;
@@ -286,8 +319,8 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         push.n_push_ctas = n;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(mq, mk, mv, p, push, int(grid), s)
-                               : launch_attn<false, false>(mq, mk, mv, p, push, int(grid), s);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s)
+                               : launch_attn<false, false>(maps, p, push, int(grid), s);
 }
 
 int pa_cp_push(const pa_cp_push_args* a, void* stream) {

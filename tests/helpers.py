@@ -79,7 +79,7 @@ class LocalCluster:
         self.capacity = need
         self.state = E.CallState()
 
-    def attention_fused_single_rank(self, q, k, v, scale=None, ctas=4, wait_ns=200_000_000):
+    def attention_fused_single_rank(self, q, k, v, scale=None, ctas=4, wait_ns=200_000_000, in_place=False):
         """World size 1 only: the exchange rides inside the attention launch (the form multi-GPU
         runs use). The pushing CTAs belong to the same launch as the CTAs that wait for them."""
         assert self.W == 1
@@ -94,17 +94,18 @@ class LocalCluster:
         n_push = E.fused_push_ctas(plan, B, sq, ctas)
         st.arrive_expect[par] += n_push
         q, k, v = E._fix(q), E._fix(k), E._fix(v)
-        push = E.build_push_args(plan, self.ws[0], par, q, k, v, n_push)
+        # in_place=False keeps the self-push so that the fused pusher path is exercised on one GPU
+        push = E.build_push_args(plan, self.ws[0], par, q, k, v, n_push, skip_self=in_place)
         out = torch.empty((B, sq, H, D), dtype=q.dtype, device=self.device).transpose(1, 2)
         scale = (1.0 / math.sqrt(D)) if scale is None else scale
         E.launch_attention(plan, self.ws[0], par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par], wait_ns,
-                           torch.cuda.current_stream(self.device).cuda_stream, out, push)
+                           torch.cuda.current_stream(self.device).cuda_stream, out, push, (q, k, v) if in_place else None)
         torch.cuda.synchronize(self.device)
         code = int(self.ws[0].status_tensor().item())
         assert code == 0, f"device status {code}"
         return out
 
-    def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000):
+    def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000, in_place=True):
         E = self.E
         B, H, sq, D = qs[0].shape
         skv = ks[0].shape[2]
@@ -120,13 +121,17 @@ class LocalCluster:
         for g in range(self.W):
             q, k, v = E._fix(qs[g]), E._fix(ks[g]), E._fix(vs[g])
             keep.append((q, k, v))
-            E.launch_push(plans[g], self.ws[g], par, q, k, v, ctas, stream)
+            pa = E.build_push_args(plans[g], self.ws[g], par, q, k, v, ctas, skip_self=in_place)
+            from paraattention_b200 import _lib as L
+            import ctypes as C
+
+            L.check(L.load().pa_cp_push(C.byref(pa), stream))
         outs = [None] * self.W
         for g in range(self.W):
             if self.U == 1:
                 outs[g] = torch.empty((B, sq, H, D), dtype=qs[g].dtype, device=self.device).transpose(1, 2)
             E.launch_attention(plans[g], self.ws[g], par, (B, H, sq, D), qs[g].dtype, skv, scale, st.arrive_expect[par],
-                               wait_ns, stream, outs[g])
+                               wait_ns, stream, outs[g], None, keep[g] if in_place else None)
         if self.U > 1:
             st.done_expect[par] += E.out_tiles_per_call(plans[0], B, sq)
             for g in range(self.W):
