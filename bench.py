@@ -136,7 +136,7 @@ def run_reference(args):
 # clocks
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
@@ -147,7 +147,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -157,7 +157,10 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
+        """Summarise the samples whose timestamps fall inside [t_begin, t_end] (time.time())."""
+        import datetime
+
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -169,19 +172,20 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx = float(parts[1])
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if t_begin is not None and not (t_begin - 0.01 <= ts <= t_end + 0.01):
+                    continue
+                sm.append(float(parts[1]))
+                mx = float(parts[2])
             except ValueError:
                 continue
-            for n, val in zip(names, parts[2:6]):
+            for n, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(n)
-        # the busiest half of the samples stands for "under load"
-        sm_sorted = sorted(sm)
-        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        load = sm
         return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
                 "samples": len(sm)}
 
@@ -215,6 +219,9 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
         mesh = dist.init_device_mesh("cuda", (R, U), mesh_dim_names=("ring", "ulysses"))
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # early: nvidia-smi needs a moment before its first sample
     q_h, k_h, v_h = make_inputs(H, S_pad)
     if world > 1:
         q_h, k_h, v_h = (x.chunk(world, dim=-2)[rank].contiguous() for x in (q_h, k_h, v_h))
@@ -240,10 +247,12 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize(dev)
 
-    def timed(fn, n_warm, n_steps):
+    def timed(fn, n_warm, n_steps, window=None):
         for _ in range(n_warm):
             fn()
         sync_all()
+        if window is not None:
+            window["begin"] = time.time()
         evs = []
         for _ in range(n_steps):
             flush.fill_(1)  # evict q/k/v and staging from L2 between timed iterations
@@ -253,17 +262,17 @@ def run_ours(args):
             e1.record()
             evs.append((e0, e1))
         sync_all()
+        if window is not None:
+            window["end"] = time.time()
         total_ms = sum(a.elapsed_time(b) for a, b in evs)
         t = torch.tensor([total_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    total_ms = timed(lambda: step(q, k, v), max(args.warmup, 3), args.steps)
-    clocks = sampler.stop() if rank == 0 else None
+    window = {}
+    total_ms = timed(lambda: step(q, k, v), max(args.warmup, 3), args.steps, window)
+    clocks = sampler.stop(window.get("begin"), window.get("end")) if rank == 0 else None
     pa.check_device_status()
 
     flops = attention_flops(H, S_pad)
@@ -330,9 +339,17 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, from the ncu
-# captures summarised under profiles/ (scaled from the captured case by heads where noted there)
-TRAFFIC_BYTES_PER_LAUNCH = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch. Captured with ncu
+# at H=24, S=8192 (profiles/attn_fwd_kernel_h24_s8192_ncu_full.md: 151.3 MB read + 33.6 MB
+# written = the q, k, v, out bytes); q, k, v and out grow linearly with S while the K/V of one
+# head (16.8 MB at S=32760) still fit the 126 MB L2, so the S=32760 rows are that capture
+# scaled by 32760/8192 (and by heads).
+_CAPTURED = 184.93e6
+TRAFFIC_BYTES_PER_LAUNCH = {
+    (24, 8192): _CAPTURED,
+    (24, 32760): _CAPTURED * 32760 / 8192,
+    (40, 32760): _CAPTURED * 32760 / 8192 * 40 / 24,
+}
 
 
 if __name__ == "__main__":
