@@ -215,6 +215,25 @@ int pa_fbc_residual_diff(const void* h1, const void* h0, const void* prev, void*
                          int32_t cols, int32_t downsample, int32_t dtype, float* result, void* scratch,
                          void* stream);
 
+/* pa_fbc_residual_diff for hosts that cannot supply scratch memory. It has no counterpart in
+ * the reference. Meant for callers that own no device allocator at the point of the call - a
+ * serving process whose GPU memory is partitioned once at start-up and frozen afterwards, or a
+ * foreign-language binding that merely passes on buffers it was handed. The partial sums live
+ * in a 4864-byte array built into the library image (one copy on every GPU that loads the
+ * library, kept until the process ends); the call itself allocates and frees nothing.
+ *
+ * Same arguments and results as pa_fbc_residual_diff, without `scratch`. Limits and rules:
+ *  - rows * cols must not exceed PA_FBC_STATIC_MAX_NUMEL (the grid is capped at 592 CTAs, and
+ *    beyond that size the per-thread fp32 partial sums would lose accuracy); larger inputs are
+ *    refused with PA_EINVAL;
+ *  - the first call on each device looks up the array's device address (that device must be
+ *    current); make that first call before any stream capture begins;
+ *  - all calls on a device share the one array: the ticket word in it is cleared in stream
+ *    order before each launch, and two calls that overlap on the GPU (different streams) race. */
+#define PA_FBC_STATIC_MAX_NUMEL (1LL << 30)
+int pa_fbc_residual_diff_static(const void* h1, const void* h0, const void* prev, void* new_resid, int64_t rows,
+                                int32_t cols, int32_t downsample, int32_t dtype, float* result, void* stream);
+
 /* out = round(a + b) (sub = 0) or round(a - b) (sub = 1), elementwise over numel 16-bit
  * elements (numel % 8 == 0, 16-byte aligned pointers): apply_prev_hidden_states_residual
  * (utils.py:237-259) and the residual formation at utils.py:443-444. */

@@ -119,6 +119,9 @@ def load() -> C.CDLL:
     lib.pa_fbc_residual_diff.restype = C.c_int
     lib.pa_fbc_residual_diff.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                          C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.pa_fbc_residual_diff_static.restype = C.c_int
+    lib.pa_fbc_residual_diff_static.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                                C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.pa_fbc_axpy.restype = C.c_int
     lib.pa_fbc_axpy.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p]
     _lib = lib

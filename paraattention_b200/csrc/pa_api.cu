@@ -415,6 +415,88 @@ int pa_fbc_residual_diff(const void* h1, const void* h0, const void* prev, void*
     return PA_OK;
 }
 
+// ---- pa_fbc_residual_diff with built-in scratch ------------------------------------------------
+// Some hosts can hand this library input and output buffers but have nothing to give it as
+// scratch: a serving process whose device memory was carved up once at start-up and then frozen,
+// or a thin binding from another runtime that only forwards pointers it was handed and owns no
+// device allocator. For them the partial-sum scratch of the cache-decision kernel lives in the
+// library image itself. The array below is file-scope device memory: every GPU that loads the
+// library carries one copy (4864 bytes) until the process exits.
+//
+// On the host, `g_fbc_static_scratch` is only a handle for the symbol, never a device address.
+// The address a kernel may use is looked up per device with cudaGetSymbolAddress (below) while
+// that device is current.
+constexpr int kFbcStaticMaxBlocks = 148 * 4;
+constexpr size_t kFbcStaticBytes = ((2 * kFbcStaticMaxBlocks + 1) * sizeof(float) + 255) / 256 * 256;
+static __device__ __align__(256) unsigned char g_fbc_static_scratch[kFbcStaticBytes];
+static void* g_fbc_static_ptr[64] = {};
+static std::mutex g_fbc_static_mu;
+
+int pa_fbc_residual_diff_static(const void* h1, const void* h0, const void* prev, void* new_resid, int64_t rows,
+                                int32_t cols, int32_t downsample, int32_t dtype, float* result, void* stream) {
+    if (!h1 || !h0 || !result) return fail(PA_EINVAL, "fbc static: h1, h0 and result must be non-NULL");
+    if (rows <= 0 || cols <= 0 || downsample < 1)
+        return fail(PA_EINVAL, "fbc static: rows, cols must be positive and downsample >= 1");
+    if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "fbc static: dtype must be PA_BF16 or PA_F16");
+    const long long numel = static_cast<long long>(rows) * cols;
+    if (numel > PA_FBC_STATIC_MAX_NUMEL)
+        return fail(PA_EINVAL, "fbc static: %lld elements exceed the limit of %lld of the built-in scratch variant; "
+                    "use pa_fbc_residual_diff with caller scratch", numel, static_cast<long long>(PA_FBC_STATIC_MAX_NUMEL));
+    // set-up, once per device, with that device current
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(PA_ECUDA, "fbc static: cudaGetDevice: %s", cudaGetErrorString(e));
+    void* sptr = nullptr;
+    {
+        std::lock_guard<std::mutex> g(g_fbc_static_mu);
+        if (g_fbc_static_ptr[dev] == nullptr) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_fbc_static_scratch);
+            if (e != cudaSuccess || p == nullptr)
+                return fail(PA_ECUDA, "fbc static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_fbc_static_ptr[dev] = p;
+        }
+        sptr = g_fbc_static_ptr[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* sc = static_cast<float*>(sptr);
+    // The array keeps whatever the last call left: the ticket word must start at zero.
+    e = cudaMemsetAsync(sc + 2 * kFbcStaticMaxBlocks, 0, sizeof(float), s);
+    if (e != cudaSuccess) return fail(PA_ECUDA, "fbc static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (downsample == 1 && numel % 8 == 0 && aligned16(h1) && aligned16(h0) && aligned16(prev) && aligned16(new_resid)) {
+        const long long n8 = numel / 8;
+        long long blocks = (n8 + pa::kFbcThreads - 1) / pa::kFbcThreads;
+        if (blocks > kFbcStaticMaxBlocks) blocks = kFbcStaticMaxBlocks;
+        float* base = sc + 2 * (kFbcStaticMaxBlocks - blocks);  // the ticket sits right behind this grid's partials
+        if (dtype == PA_BF16)
+            pa::fbc_residual_diff_kernel<true><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint4*>(h1), static_cast<const uint4*>(h0), static_cast<const uint4*>(prev),
+                static_cast<uint4*>(new_resid), n8, base, result);
+        else
+            pa::fbc_residual_diff_kernel<false><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint4*>(h1), static_cast<const uint4*>(h0), static_cast<const uint4*>(prev),
+                static_cast<uint4*>(new_resid), n8, base, result);
+    } else {
+        const int cols_ds = (cols + downsample - 1) / downsample;
+        const long long n = static_cast<long long>(rows) * cols_ds;
+        long long blocks = (n + pa::kFbcThreads - 1) / pa::kFbcThreads;
+        if (blocks > kFbcStaticMaxBlocks) blocks = kFbcStaticMaxBlocks;
+        float* base = sc + 2 * (kFbcStaticMaxBlocks - blocks);
+        if (dtype == PA_BF16)
+            pa::fbc_residual_diff_strided_kernel<true><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint16_t*>(h1), static_cast<const uint16_t*>(h0), static_cast<const uint16_t*>(prev),
+                static_cast<uint16_t*>(new_resid), rows, cols, downsample, base, result);
+        else
+            pa::fbc_residual_diff_strided_kernel<false><<<int(blocks), pa::kFbcThreads, 0, s>>>(
+                static_cast<const uint16_t*>(h1), static_cast<const uint16_t*>(h0), static_cast<const uint16_t*>(prev),
+                static_cast<uint16_t*>(new_resid), rows, cols, downsample, base, result);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "fbc static launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
 int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t sub, int32_t dtype, void* stream) {
     if (!a || !b || !out) return fail(PA_EINVAL, "axpy: NULL pointer");
     if (numel <= 0 || numel % 8 != 0) return fail(PA_EINVAL, "axpy: numel must be a positive multiple of 8");
