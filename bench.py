@@ -43,6 +43,10 @@ def parse_args():
     ap.add_argument("--heads", type=int, default=24)
     ap.add_argument("--seq", type=int, default=32760)
     ap.add_argument("--mesh", default=None, help="UxR, default Nx1 (all Ulysses)")
+    ap.add_argument("--workload", default="attention", choices=["attention", "flux", "wan", "hunyuan"],
+                    help="attention = the headline op benchmark; the others time one transformer forward")
+    ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the block count (quick runs)")
+    ap.add_argument("--fbcache", type=float, default=0.0, help="DiT workloads: First-Block-Cache threshold (0 = off)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -352,9 +356,107 @@ TRAFFIC_BYTES_PER_LAUNCH = {
 }
 
 
+# ------------------------------------------------------------------------------------------
+# second metric: transformer forward latency of the shape-only DiTs under the adapters
+# ------------------------------------------------------------------------------------------
+def run_dit(args):
+    """--workload flux|wan|hunyuan: ms per transformer forward (one denoising step) of the
+    shape-only model at full size, random bf16 weights, under parallelize_transformer
+    (and apply_cache_on_transformer when --fbcache > 0). Prints one JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    import paraattention_b200 as pa
+    from paraattention_b200.context_parallel import init_context_parallel_mesh
+    from paraattention_b200.context_parallel.diffusers_adapters import parallelize_transformer
+    from paraattention_b200.first_block_cache import utils as fbc
+    from paraattention_b200.first_block_cache.diffusers_adapters import apply_cache_on_transformer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    U, R = (int(x) for x in args.mesh.lower().split("x")) if args.mesh else (world, 1)
+    mesh = init_context_parallel_mesh("cuda", max_ring_dim_size=R if R > 1 else None)
+    dt = torch.bfloat16
+    layers = args.layers
+    torch.manual_seed(0)
+    torch.set_default_dtype(dt)  # build the weights directly in bf16
+    with torch.device(dev):
+        if args.workload == "flux":
+            from paraattention_b200.shape_models import FluxShapedTransformer2DModel
+
+            kw = {} if layers is None else dict(num_layers=max(1, layers // 3), num_single_layers=layers - max(1, layers // 3))
+            model = FluxShapedTransformer2DModel(**kw).to(dt)
+            n_img, n_txt = 4096, 512
+            hw = 64
+            ys, xs = torch.meshgrid(torch.arange(hw), torch.arange(hw), indexing="ij")
+            inputs = dict(hidden_states=torch.randn(1, n_img, 64).to(dt), encoder_hidden_states=torch.randn(1, n_txt, 4096).to(dt),
+                          pooled_projections=torch.randn(1, 768).to(dt), timestep=torch.tensor([500.0]),
+                          img_ids=torch.stack([torch.zeros_like(ys), ys, xs], -1).reshape(-1, 3).float(),
+                          txt_ids=torch.zeros(n_txt, 3), guidance=torch.tensor([3.5]), return_dict=False)
+            call = lambda: model(**inputs)[0]
+            desc = "FLUX.1-dev-shaped MMDiT, 512 text + 4096 image tokens"
+        elif args.workload == "wan":
+            from paraattention_b200.shape_models_video import WanShapedTransformer3DModel
+
+            model = WanShapedTransformer3DModel(**({} if layers is None else dict(num_layers=layers))).to(dt)
+            x, enc = torch.randn(1, 16, 21, 60, 104).to(dt), torch.randn(1, 512, 4096).to(dt)
+            t = torch.tensor([500.0])
+            call = lambda: model(x, t, enc, return_dict=False)[0]
+            desc = "Wan 2.1 14B-shaped DiT, 32760 video tokens + 512-token cross-attention"
+        else:
+            from paraattention_b200.shape_models_hunyuan import HunyuanVideoShapedTransformer3DModel
+
+            kw = {} if layers is None else dict(num_layers=max(1, layers // 3), num_single_layers=layers - max(1, layers // 3))
+            model = HunyuanVideoShapedTransformer3DModel(**kw).to(dt)
+            x, enc = torch.randn(1, 16, 33, 90, 160).to(dt), torch.randn(1, 256, 4096).to(dt)
+            t, mask, pooled, g = torch.tensor([500.0]), torch.ones(1, 256), torch.randn(1, 768).to(dt), torch.tensor([6.0])
+            call = lambda: model(x, t, enc, mask, pooled, guidance=g, return_dict=False)[0]
+            desc = "HunyuanVideo-shaped DiT, 118800 video + 256 text tokens"
+    torch.set_default_dtype(torch.float32)
+    n_blocks = sum(1 for _ in model.modules() if type(_).__name__.endswith("Block"))
+    parallelize_transformer(model, mesh=mesh)
+    if args.fbcache > 0:
+        apply_cache_on_transformer(model)
+    ctx = fbc.create_cache_context(residual_diff_threshold=args.fbcache)
+    times = []
+    with torch.no_grad(), fbc.cache_context(ctx):
+        for i in range(max(args.warmup, 1) + args.steps):
+            torch.cuda.synchronize(dev)
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = call()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            if i >= max(args.warmup, 1):
+                t_ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+                dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+                times.append(float(t_ms.item()))
+    pa.check_device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "dit_step_latency_ms", "value": statistics.median(times), "unit": "ms", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": statistics.mean(times),
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": desc, "blocks": n_blocks, "mesh": f"{U}x{R} (ulysses x ring)",
+                       "fbcache_threshold": args.fbcache, "weights": "random init", "output_finite": bool(torch.isfinite(out.float()).all())},
+        }), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload != "attention":
+        run_dit(a)
     else:
         run_ours(a)
