@@ -22,8 +22,8 @@ class attention:
 class cp:
     """Knobs of the NVLink exchange that have no counterpart in the reference."""
 
-    # CTAs per destination rank in the push kernel (more CTAs = more NVLink stores in flight)
-    push_ctas_per_dest = int(os.getenv("PA_B200_PUSH_CTAS", "16"))
+    # how many leading CTAs of the attention grid do the exchange (0 = choose from the bytes to send)
+    push_ctas_per_dest = int(os.getenv("PA_B200_PUSH_CTAS", "0"))
     # device-side bound on every wait for a peer, in nanoseconds
     wait_limit_ns = int(os.getenv("PA_B200_WAIT_LIMIT_NS", str(5_000_000_000)))
 
