@@ -131,6 +131,17 @@ typedef struct pa_cp_attn_args {
     int64_t v_local_stride[3];
     int32_t local_head_offset;
     int32_t local_total_heads;
+    /* Causal masking over the whole (sharded) sequence: when is_causal != 0, row i of query
+     * chunk c sits at global position q_pos[c] + i and row j of key/value chunk c at
+     * kv_pos[c] + j; a key is visible to a query iff its position is not later. Key/value tiles
+     * no query of a CTA can see are skipped (neither waited for nor read). This replaces the
+     * per-step is_causal / skip logic of torch:_templated_ring_attention (torch:...:394-437)
+     * and covers the Ulysses case, where every rank sees whole sequences. Query rows that see
+     * no key at all come out as zeros with an LSE of -inf. */
+    int32_t is_causal;
+    int32_t pad_;
+    int64_t q_pos[PA_MAX_CHUNKS];
+    int64_t kv_pos[PA_MAX_CHUNKS];
 } pa_cp_attn_args;
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);

@@ -240,16 +240,17 @@ def fused_push_ctas(plan: CpPlan, B: int, sq: int, ctas: int) -> int:
 
 def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
                      arrive_expect: int, wait_ns: int, stream: int, out_local: Optional[torch.Tensor],
-                     push: Optional["L.CpPushArgs"] = None, local_qkv=None) -> None:
+                     push: Optional["L.CpPushArgs"] = None, local_qkv=None, is_causal: bool = False) -> None:
     """Build the arguments (``build_attention_args``) and launch pa_cp_attn_fwd."""
     a = build_attention_args(plan, ws, par, shape, dtype, skv, scale, arrive_expect, wait_ns, out_local, push,
-                             local_qkv)
+                             local_qkv, is_causal)
     L.check(L.load().pa_cp_attn_fwd(C.byref(a), stream))
 
 
 def build_attention_args(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
                          arrive_expect: int, wait_ns: int, out_local: Optional[torch.Tensor],
-                         push: Optional["L.CpPushArgs"] = None, local_qkv=None) -> "L.CpAttnArgs":
+                         push: Optional["L.CpPushArgs"] = None, local_qkv=None,
+                         is_causal: bool = False) -> "L.CpAttnArgs":
     """Arguments of pa_cp_attn_fwd for this rank. ``out_local`` (ring-only meshes) receives the result in
     place; otherwise tiles go to the owners' output staging buffers. With ``push`` the launch
     also performs this rank's part of the exchange (fused form). ``local_qkv`` = this rank's own
@@ -292,6 +293,15 @@ def build_attention_args(plan: CpPlan, ws: Workspace, par: int, shape, dtype: to
             a.q_local_stride[d], a.k_local_stride[d], a.v_local_stride[d] = ql.stride(d), kl.stride(d), vl.stride(d)
         a.local_head_offset = plan.u * hl
         a.local_total_heads = H
+    if is_causal:
+        # The sequence is sharded in flat-rank order: the Ulysses exchange concatenates the
+        # shards of a group in ulysses-index order (src/para_attn/para_attn_interface.py:60-72)
+        # and causal ring attention orders blocks by ring index (torch:...:394-437).
+        a.is_causal = 1
+        for c in range(plan.ulysses):
+            a.q_pos[c] = plan.flat(c, plan.r) * sq
+        for c in range(plan.world):
+            a.kv_pos[c] = c * skv
     return a
 
 
@@ -366,8 +376,10 @@ class CpEngine:
         if st != 0:
             raise L.PaError(L.PA_ETIMEDOUT, L.DEV_STATUS_NAMES.get(st, f"device status {st}"))
 
-    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float]) -> torch.Tensor:
-        """q: [B, H, s_q, 128], k/v: [B, H, s_kv, 128] local shards -> [B, H, s_q, 128] local output."""
+    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float],
+                  is_causal: bool = False) -> torch.Tensor:
+        """q: [B, H, s_q, 128], k/v: [B, H, s_kv, 128] local shards -> [B, H, s_q, 128] local output.
+        ``is_causal`` masks over the whole sequence, shards taken in flat-rank order."""
         B, H, sq, D = q.shape
         skv = k.shape[2]
         plan = CpPlan(self.ulysses, self.ring, self.u, self.r, H)
@@ -398,12 +410,12 @@ class CpEngine:
         out_local = None
         if self.ulysses == 1:
             out_local = torch.empty((B, sq, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
-        key = (B, H, sq, skv, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride())
+        key = (B, H, sq, skv, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(), is_causal)
         ent = self._launch_cache.get(key)
         if ent is None:
             push = build_push_args(plan, ws, par, q, k, v, n_push)
             a = build_attention_args(plan, ws, par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par],
-                                     wait_ns, out_local, push, (q, k, v))
+                                     wait_ns, out_local, push, (q, k, v), is_causal)
             which = [js.tensor for js in plan.push_jobs(skip_self=True)]
             ent = (a, push, which)
             if len(self._launch_cache) > 64:
@@ -419,6 +431,16 @@ class CpEngine:
             if out_local is not None:
                 a.out[0] = out_local.data_ptr()
         L.check(L.load().pa_cp_attn_fwd(C.byref(a), main.cuda_stream))
+        if is_causal:
+            # A causal kernel does not wait for the chunks it cannot see, so an early rank could
+            # run two calls ahead and overwrite staging memory a later rank still reads. Waiting
+            # for every rank's arrival counter keeps the ranks within one call of each other,
+            # which is what the two staging parities allow.
+            lay = ws.layout
+            others = [s for s in range(self.world) if s != plan.rank]  # nobody counts into its own slot
+            flags = (C.c_void_p * len(others))(*[ws.base + lay.off_arrive[par] + 4 * s for s in others])
+            L.check(L.load().pa_flag_wait(flags, len(others), st.arrive_expect[par], ws.base + lay.off_status,
+                                          wait_ns, 3, main.cuda_stream))
         if out_local is not None:
             return out_local
 

@@ -59,6 +59,8 @@ class CpAttnArgs(C.Structure):
         ("q_local", C.c_void_p), ("k_local", C.c_void_p), ("v_local", C.c_void_p),
         ("q_local_stride", C.c_int64 * 3), ("k_local_stride", C.c_int64 * 3), ("v_local_stride", C.c_int64 * 3),
         ("local_head_offset", C.c_int32), ("local_total_heads", C.c_int32),
+        ("is_causal", C.c_int32), ("pad_", C.c_int32),
+        ("q_pos", C.c_int64 * PA_MAX_CHUNKS), ("kv_pos", C.c_int64 * PA_MAX_CHUNKS),
     ]
 
 

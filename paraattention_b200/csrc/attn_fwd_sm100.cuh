@@ -89,6 +89,11 @@ struct AttnParams {
     unsigned long long wait_ns;
     // chunks read in place from this rank's own tensors instead of the staging buffers (-1: none)
     int q_local_chunk, kv_local_chunk, local_head0;
+    // causal masking (kernels instantiated with kCausal read these; `causal` selects them): a key at global position kv_pos[chunk] + col is visible to the query at
+    // global position q_pos[chunk] + row iff it is not later (top-left aligned, as torch SDPA)
+    int causal;
+    long long q_pos[PA_MAX_CHUNKS];
+    long long kv_pos[PA_MAX_CHUNKS];
     // debug instantiation only
     float* dbg_s;      // raw S of CTA 0: [tile][kv tile][row][col]
     int v_lbo, v_sbo;  // B descriptor of V (bytes)
@@ -129,7 +134,7 @@ __device__ __forceinline__ void pair_sync(int id) {
     asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
 }
 
-template <bool kBF16, bool kDebug>
+template <bool kBF16, bool kDebug, bool kCausal>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ql,
@@ -195,8 +200,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ---- which work unit: (batch, head, query chunk, pair of query tiles) -------------------
     const int pairs_per_chunk = (p.q_rows + 2 * kTileM - 1) / (2 * kTileM);
     int unit = blockIdx.x;
-    const int pair = unit % pairs_per_chunk;
+    int pair = unit % pairs_per_chunk;
     unit /= pairs_per_chunk;
+    // the late query tiles of a causal run see the most keys: schedule them first
+    if (kCausal) pair = pairs_per_chunk - 1 - pair;
     const int head = unit % p.heads;
     unit /= p.heads;
     const int bidx = unit % p.batch;
@@ -205,7 +212,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int row0 = pair * 2 * kTileM;
 
     const int tiles_per_chunk = (p.kv_rows + kTileN - 1) / kTileN;
-    const int n_tiles = tiles_per_chunk * p.n_kv_chunks;
+    // Causal runs skip the key/value tiles that lie wholly after this CTA's last query row. All
+    // roles derive the same tile list from tiles_in_chunk().
+    const long long q_last = kCausal ? p.q_pos[qc] + min(row0 + 2 * kTileM, p.q_rows) - 1 : 0;
+    auto tiles_in_chunk = [&](int c) -> int {
+        if (!kCausal) return tiles_per_chunk;
+        const long long visible = q_last - p.kv_pos[c] + 1;  // key rows of this chunk some query may see
+        if (visible <= 0) return 0;
+        const long long t = (visible + kTileN - 1) / kTileN;
+        return t < tiles_per_chunk ? static_cast<int>(t) : tiles_per_chunk;
+    };
+    int n_tiles = 0;
+    for (int c = 0; c < p.n_kv_chunks; ++c) n_tiles += tiles_in_chunk(c);
     const uint64_t pipe_limit = p.wait_ns + 1000000000ull;
 
     // Fused exchange: the leading CTAs of the grid (always resident in the first wave, and
@@ -227,7 +245,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp >= kSoftmaxWarps) setmaxnreg_dec<kRegsControl>();
     if (warp == kTmaWarp) {
         // =============================== TMA producer ======================================
-        if (lane == 0) {
+        if (lane == 0 && n_tiles > 0) {
             int issued = 0;
             bool ok = true;
             const bool q_in_place = (qc == p.q_local_chunk);
@@ -253,6 +271,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
                 int c = p.kv_first + ci;
                 if (c >= p.n_kv_chunks) c -= p.n_kv_chunks;
+                const int tiles_c = tiles_in_chunk(c);
+                if (tiles_c == 0) continue;
                 const bool kv_in_place = (c == p.kv_local_chunk);
                 if (!kv_in_place && p.kv_flag[c] != nullptr) {
                     ok = flag_wait_ge(p.kv_flag[c], p.flag_expect, s_abort, p.status, p.wait_ns,
@@ -264,7 +284,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const CUtensorMap* mv = kv_in_place ? &tm_vl : &tm_v;
                 const int hk = kv_in_place ? head + p.local_head0 : head;
                 const int ck = kv_in_place ? 0 : c;
-                for (int t = 0; t < tiles_per_chunk; ++t, ++j) {
+                for (int t = 0; t < tiles_c; ++t, ++j) {
                     const int st = j & 1;
                     const uint32_t ph = (j >> 1) & 1;
                     const uint32_t bk = smem_u32(&ctl->k_full[st]);
@@ -308,7 +328,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // =============================== MMA issuer ========================================
         // The issuer must keep ahead of the tensor core (64 cycles per 128x128x16 MMA): the
         // k-step loops are unrolled and every descriptor is a base plus a constant.
-        if (lane == 0) {
+        if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN);
             constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kHeadDim);
             constexpr uint32_t idesc_pv64 = make_idesc_f16(kBF16, true, kTileM, 64);
@@ -430,9 +450,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float l_sum = 0.f;  // over my columns only
         bool ok = true;
         int j = 0;
+        const long long q_here = kCausal ? p.q_pos[qc] + row0 + t * kTileM + row_in_tile : 0;  // my row's global position
         for (int ci = 0; ci < p.n_kv_chunks; ++ci) {
-            for (int tk = 0; tk < tiles_per_chunk; ++tk, ++j) {
-                const int valid = min(kTileN, p.kv_rows - tk * kTileN) - half * 64;  // of my 64 columns
+            int c_kv = p.kv_first + ci;
+            if (c_kv >= p.n_kv_chunks) c_kv -= p.n_kv_chunks;
+            const int tiles_c = tiles_in_chunk(c_kv);
+            for (int tk = 0; tk < tiles_c; ++tk, ++j) {
+                int valid = min(kTileN, p.kv_rows - tk * kTileN) - half * 64;  // of my 64 columns
+                if (kCausal) {
+                    const long long lim = q_here - (p.kv_pos[c_kv] + tk * kTileN + half * 64) + 1;
+                    valid = static_cast<int>(lim < valid ? (lim < 0 ? 0 : lim) : valid);
+                }
                 dbg_stamp<kDebug>(p, t, j, 0, stamper);
                 // A wait that gives up does not leave the loop: the two partner warps must meet at
                 // every pair barrier below, and once the abort word is set no wait blocks any more.
@@ -480,7 +508,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const float m_new = fmax3(mine, ctl->xch[j & 1][t][half ^ 1][row_in_tile], m_ref);
                 const bool grow = (m_new - m_ref) * sl > kRescaleThreshold;
                 if (__any_sync(0xffffffffu, grow)) {  // same decision in both partner warps
-                    const float alpha = ex2_approx((m_ref - m_new) * sl);
+                    // (a row that has seen no visible key yet keeps m = -inf: scale by 1, not by NaN)
+                    const float alpha = (kCausal && m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl);
                     l_sum *= alpha;
                     m_ref = m_new;
                     if (j > 0) {
@@ -506,7 +535,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         tc_fence_after();
                     }
                 }
-                const float neg = -m_ref * sl;
+                const float neg = (kCausal && m_ref == -INFINITY) ? 0.0f : -m_ref * sl;
                 dbg_stamp<kDebug>(p, t, j, 3, stamper);
                 // p = 2^(s*sl - m*sl) in packed fp32x2 arithmetic. The exponentials are split between
                 // the special-function unit and an FMA-pipe polynomial so that neither pipe alone
@@ -557,7 +586,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 dbg_stamp<kDebug>(p, t, j, 5, stamper);
             }
         }
-        ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
+        // (a CTA whose queries see no key at all writes zeros and an LSE of -inf)
+        const bool empty = (n_tiles == 0);
+        if (!empty)
+            ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
         // row sum over both halves
         ctl->xch[n_tiles & 1][t][half][row_in_tile] = l_sum;
         pair_sync(pair_bar);
@@ -566,7 +598,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_fence_after();
             const int row = row0 + t * kTileM + row_in_tile;
             const bool in_range = row < p.q_rows;
-            const float inv = 1.0f / l_row;
+            const float inv = empty ? 0.0f : 1.0f / l_row;
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
                              (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
                               static_cast<long long>(row) * p.o_ss) + half * 64;
@@ -576,6 +608,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 tmem_ld32(tO + c * 32, o);
                 tc_wait_ld();
                 tmem_ld_fence(o);
+                if (empty) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;
+                }
                 if (in_range) {
 #pragma unroll
                     for (int v4 = 0; v4 < 4; ++v4) {

@@ -75,10 +75,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int rows, int heads,
     return PA_OK;
 }
 
-template <bool kBF16, bool kDebug>
-int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
+template <bool kBF16, bool kDebug, bool kCausal>
+int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream) {
-    auto kern = pa::attn_fwd_kernel<kBF16, kDebug>;
+    auto kern = pa::attn_fwd_kernel<kBF16, kDebug, kCausal>;
     static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
     {
@@ -97,11 +97,20 @@ int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::Push
     return PA_OK;
 }
 
-int check_common(int head_dim, int dtype, float scale, int is_causal) {
+template <bool kBF16, bool kDebug>
+int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
+                cudaStream_t stream) {
+    if (p.causal) {
+        if (kDebug) return fail(PA_ENOTSUP, "the debug hooks are built without causal masking");
+        return launch_attn_inst<kBF16, false, true>(maps, p, push, grid, stream);
+    }
+    return launch_attn_inst<kBF16, kDebug, false>(maps, p, push, grid, stream);
+}
+
+int check_common(int head_dim, int dtype, float scale) {
     if (head_dim != 128) return fail(PA_ENOTSUP, "head_dim %d: only 128 is built", head_dim);
     if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "dtype %d: expected PA_BF16 or PA_F16", dtype);
     if (!(scale > 0.f) || !std::isfinite(scale)) return fail(PA_EINVAL, "scale must be positive and finite");
-    if (is_causal) return fail(PA_ENOTSUP, "causal masking is not built");
     return PA_OK;
 }
 
@@ -118,7 +127,7 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     if (!a->q || !a->k || !a->v || !a->out) return fail(PA_EINVAL, "q, k, v and out must be non-NULL");
     if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0)
         return fail(PA_EINVAL, "batch, heads, seq_q and seq_kv must be positive");
-    int rc = check_common(a->head_dim, a->dtype, a->scale, a->is_causal);
+    int rc = check_common(a->head_dim, a->dtype, a->scale);
     if (rc != PA_OK) return rc;
     rc = out_checks(a->out, a->o_stride);
     if (rc != PA_OK) return rc;
@@ -145,6 +154,7 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     p.q_rows = a->seq_q;
     p.n_kv_chunks = 1;
     p.kv_rows = a->seq_kv;
+    p.causal = a->is_causal ? 1 : 0;  // both sequences start at position 0: key j visible to query i iff j <= i
     p.scale = a->scale;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     p.out[0] = a->out;
@@ -231,7 +241,7 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         return fail(PA_EINVAL, "chunk counts must be in [1, %d]", PA_MAX_CHUNKS);
     if (a->q_first < 0 || a->q_first >= a->n_q_chunks || a->kv_first < 0 || a->kv_first >= a->n_kv_chunks)
         return fail(PA_EINVAL, "q_first / kv_first out of range");
-    int rc = check_common(a->head_dim, a->dtype, a->scale, 0);
+    int rc = check_common(a->head_dim, a->dtype, a->scale);
     if (rc != PA_OK) return rc;
     for (int c = 0; c < a->n_q_chunks; ++c) {
         if (a->out[c] == nullptr) return fail(PA_EINVAL, "out[%d] is NULL", c);
@@ -285,6 +295,17 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     p.n_kv_chunks = a->n_kv_chunks;
     p.kv_rows = a->kv_rows;
     p.kv_first = a->kv_first;
+    p.causal = a->is_causal ? 1 : 0;
+    if (p.causal) {
+        for (int c = 0; c < a->n_q_chunks; ++c) {
+            if (a->q_pos[c] < 0) return fail(PA_EINVAL, "q_pos[%d] is negative", c);
+            p.q_pos[c] = a->q_pos[c];
+        }
+        for (int c = 0; c < a->n_kv_chunks; ++c) {
+            if (a->kv_pos[c] < 0) return fail(PA_EINVAL, "kv_pos[%d] is negative", c);
+            p.kv_pos[c] = a->kv_pos[c];
+        }
+    }
     p.scale = a->scale;
     p.scale_log2 = a->scale * 1.4426950408889634f;
     for (int c = 0; c < PA_MAX_CHUNKS; ++c) {

@@ -36,8 +36,6 @@ def _check_inputs(query, key, value, attn_mask, dropout_p, is_causal):
         raise NotImplementedError("attn_mask is not built into the sm_100a attention kernel")
     if dropout_p != 0.0:
         raise NotImplementedError("dropout_p must be 0: the library is forward/inference only")
-    if is_causal:
-        raise NotImplementedError("is_causal is not built into the sm_100a attention kernel")
     if query.shape[-1] != 128 or key.shape[-1] != 128 or value.shape[-1] != 128:
         raise NotImplementedError(f"head_dim {query.shape[-1]}: only 128 is built")
     assert key.shape[:2] == query.shape[:2] and value.shape == key.shape, "mismatched batch/head/key shapes"
@@ -54,7 +52,7 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
 
 
 def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: bool,
-                          status: Optional[torch.Tensor] = None):
+                          status: Optional[torch.Tensor] = None, is_causal: bool = False):
     """Launch pa_attn_fwd on the current stream. Output memory is [B, S, H, D] viewed as
     [B, H, S, D], the layout PyTorch's flash backend returns, so that the usual
     ``transpose(1, 2).flatten(2)`` that follows attention is free."""
@@ -68,7 +66,7 @@ def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: b
     a.lse = lse.data_ptr() if lse is not None else None
     a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = B, H, Sq, Skv, D
     a.dtype = _DTYPES[query.dtype]
-    a.is_causal = 0
+    a.is_causal = 1 if is_causal else 0
     a.scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
     for i in range(3):
         a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
@@ -90,7 +88,7 @@ def attention_forward_with_lse(
     scale: Optional[float] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     _check_inputs(query, key, value, attn_mask, dropout_p, is_causal)
-    out, lse = raw_attention_forward(query, key, value, scale, True)
+    out, lse = raw_attention_forward(query, key, value, scale, True, is_causal=is_causal)
     return out, lse
 
 
@@ -114,7 +112,7 @@ def attention_forward(
     scale: Optional[float] = None,
 ) -> torch.Tensor:
     _check_inputs(query, key, value, attn_mask, dropout_p, is_causal)
-    out, _ = raw_attention_forward(query, key, value, scale, False)
+    out, _ = raw_attention_forward(query, key, value, scale, False, is_causal=is_causal)
     return out
 
 

@@ -44,7 +44,6 @@ def _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal) -> bool:
         and value.shape[-1] == 128
         and attn_mask is None
         and dropout_p == 0.0
-        and not is_causal
     )
 
 
@@ -52,7 +51,7 @@ def _local_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal
     """The non-parallel SDPA at the bottom of every mode (state "none" of the reference,
     src/para_attn/para_attn_interface.py:468-475)."""
     if _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal):
-        return para_attn_ops.attention_forward(query, key, value, scale=scale)
+        return para_attn_ops.attention_forward(query, key, value, is_causal=is_causal, scale=scale)
     if get_force_dispatch_to_custom_ops():
         return para_attn_ops.attention_forward(
             query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale)
@@ -60,17 +59,17 @@ def _local_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal
         query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale)
 
 
-def _cp_attention(query, key, value, scale, *, flat_group, ulysses, ring, u, r):
+def _cp_attention(query, key, value, scale, *, flat_group, ulysses, ring, u, r, is_causal=False):
     assert query.device.type == "cuda", "Must be CUDA tensors"
     eng = _cp_engine.get_engine(flat_group, ulysses, ring, u, r, query.device)
-    return eng.attention(query, key, value, scale)
+    return eng.attention(query, key, value, scale, is_causal=bool(is_causal))
 
 
 def _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, what):
     if not _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal):
         raise NotImplementedError(
             f"{what}: the context-parallel kernel is built for CUDA bf16/f16 tensors with head_dim 128, "
-            "no mask, no dropout, non-causal")
+            "no mask, no dropout")
 
 
 def ulysses_attn_func(
@@ -104,7 +103,7 @@ def ulysses_attn_func(
             "kernel and cannot wrap a foreign attention function")
     _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "ulysses_attn_func")
     return _cp_attention(query, key, value, scale, flat_group=pg, ulysses=world_size, ring=1,
-                         u=DP.get_rank(pg), r=0)
+                         u=DP.get_rank(pg), r=0, is_causal=is_causal)
 
 
 def ring_attn_func(
@@ -127,7 +126,7 @@ def ring_attn_func(
     assert attn_mask is None, "attn_mask is not supported in ring_attn_func when world_size > 1"
     _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "ring_attn_func")
     return _cp_attention(query, key, value, scale, flat_group=pg, ulysses=1, ring=world_size, u=0,
-                         r=DP.get_rank(pg))
+                         r=DP.get_rank(pg), is_causal=is_causal)
 
 
 def unified_attn_func(
@@ -160,7 +159,7 @@ def unified_attn_func(
     assert flat_group is not None, "a process group spanning the ulysses x ring ranks is required"
     _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "unified attention")
     return _cp_attention(query, key, value, scale, flat_group=flat_group, ulysses=U, ring=R,
-                         u=DP.get_rank(ulysses_mesh), r=DP.get_rank(ring_mesh))
+                         u=DP.get_rank(ulysses_mesh), r=DP.get_rank(ring_mesh), is_causal=is_causal)
 
 
 def in_batch_attn_func(

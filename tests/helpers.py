@@ -105,7 +105,7 @@ class LocalCluster:
         assert code == 0, f"device status {code}"
         return out
 
-    def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000, in_place=True):
+    def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000, in_place=True, is_causal=False):
         E = self.E
         B, H, sq, D = qs[0].shape
         skv = ks[0].shape[2]
@@ -131,7 +131,7 @@ class LocalCluster:
             if self.U == 1:
                 outs[g] = torch.empty((B, sq, H, D), dtype=qs[g].dtype, device=self.device).transpose(1, 2)
             E.launch_attention(plans[g], self.ws[g], par, (B, H, sq, D), qs[g].dtype, skv, scale, st.arrive_expect[par],
-                               wait_ns, stream, outs[g], None, keep[g] if in_place else None)
+                               wait_ns, stream, outs[g], None, keep[g] if in_place else None, is_causal)
         if self.U > 1:
             st.done_expect[par] += E.out_tiles_per_call(plans[0], B, sq)
             for g in range(self.W):

@@ -13,7 +13,7 @@ from helpers import (assert_attention_close, assert_lse_close, bf16_from_bits, o
 pytestmark = pytest.mark.gpu
 
 
-def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None):
+def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is_causal=False):
     from paraattention_b200 import _lib as L
 
     lib = L.load()
@@ -27,6 +27,7 @@ def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None):
     a.batch, a.heads, a.seq_q, a.seq_kv, a.head_dim = B, H, Sq, k.shape[2], D
     a.dtype = L.PA_BF16 if q.dtype == torch.bfloat16 else L.PA_F16
     a.scale = 1.0 / math.sqrt(D) if scale is None else scale
+    a.is_causal = int(is_causal)
     for i in range(3):
         a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
     a.status = status.data_ptr() if status is not None else None
@@ -44,6 +45,37 @@ SHAPES = [
     (1, 2, 4095, 4095),    # the per-rank shard length of 32760 tokens over 8 ranks
     (1, 4, 333, 2048),
 ]
+
+
+CAUSAL_SHAPES = [
+    (1, 1, 128, 128),
+    (1, 1, 1, 1),
+    (1, 2, 127, 129),      # more keys than queries: the tail of the keys is never visible
+    (1, 2, 300, 65),       # more queries than keys: late queries see every key
+    (2, 3, 515, 515),
+    (1, 2, 1000, 2048),
+    (1, 2, 4095, 4095),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,Sq,Skv", CAUSAL_SHAPES)
+def test_abi_causal_attention_matches_oracle(B, H, Sq, Skv, dtype):
+    """Top-left aligned causal mask (key j visible to query i iff j <= i), as torch SDPA's
+    is_causal and the oracle's."""
+    if dtype == torch.float16 and Sq > 600:
+        pytest.skip("the large shapes run in bf16 only")
+    q, k, v = seeded_qkv(B, H, Sq, Skv, seed=Sq * 11 + Skv, dtype=dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc, out, lse = _abi_attention(q, k, v, status=status, is_causal=True)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref_out, ref_lse = O.sdpa_with_lse(*(t.float().cpu().numpy() for t in (q, k, v)), is_causal=True)
+    assert_attention_close(out, ref_out, f"causal B{B} H{H} Sq{Sq} Skv{Skv}")
+    assert_lse_close(lse, ref_lse)
+    # the first query row sees key 0 only: its output is exactly v[0]
+    assert torch.equal(out[:, :, 0], v[:, :, 0])
 
 
 @pytest.mark.parametrize("B,H,Sq,Skv", SHAPES)
@@ -125,8 +157,11 @@ def test_custom_ops_and_modes_single_rank():
     assert_lse_close(lse, ref_lse)
     assert_attention_close(ops.attention_forward(q, k, v), ref_out, "attention_forward")
     assert_attention_close(pa.in_batch_attn_func(q, k, v), ref_out, "in_batch b=1")
-    with pytest.raises(NotImplementedError):
-        ops.attention_forward(q, k, v, is_causal=True)
+    causal_out, causal_lse = O.sdpa_with_lse(*(t.float().cpu().numpy() for t in (q, k, v)), is_causal=True)
+    assert_attention_close(ops.attention_forward(q, k, v, is_causal=True), causal_out, "attention_forward causal")
+    out, lse = torch.ops.para_attn.attention_forward_with_lse(q, k, v, is_causal=True)
+    assert_attention_close(out, causal_out, "custom op causal")
+    assert_lse_close(lse, causal_lse)
 
 
 def test_merge_kernel_matches_oracle():

@@ -33,6 +33,38 @@ def test_world2_against_reference_outputs(golden_dir, name, U, R):
         assert_attention_close(outs[rank], g[name][rank], f"{name} rank {rank}")
 
 
+@pytest.mark.parametrize("name,U,R", [("ulysses_causal", 2, 1), ("ring_causal", 1, 2)])
+def test_world2_causal_against_reference_outputs(golden_dir, name, U, R):
+    g = np.load(golden_dir / "cp_attention_w2.npz")
+    qs, ks, vs = _golden_shards(golden_dir, ("q", "k", "v"), 2)
+    outs = LocalCluster(U, R).attention(qs, ks, vs, is_causal=True)
+    for rank in range(2):
+        assert_attention_close(outs[rank], g[name][rank], f"{name} rank {rank}")
+
+
+@pytest.mark.parametrize("U,R,H,S", [(8, 1, 8, 8 * 300), (4, 2, 8, 8 * 131), (2, 4, 4, 8 * 257), (1, 8, 2, 8 * 129)])
+def test_world8_meshes_causal_against_oracle(U, R, H, S):
+    """Causal masking over the sharded sequence: equal to the oracle's composition of Ulysses
+    and causal ring attention, and to plain causal attention over the whole sequence."""
+    W = U * R
+    q, k, v = seeded_qkv(1, H, S, S, seed=U * 10 + R + 100)
+    qs, ks, vs = ([t.contiguous() for t in x.chunk(W, dim=-2)] for x in (q, k, v))
+    cluster = LocalCluster(U, R)
+    outs = cluster.attention(qs, ks, vs, is_causal=True)
+    ref = O.unified_attention([t.float().cpu().numpy() for t in qs], [t.float().cpu().numpy() for t in ks],
+                              [t.float().cpu().numpy() for t in vs], ulysses=U, ring=R, is_causal=True)
+    whole, _ = O.sdpa_with_lse(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(),
+                               is_causal=True)
+    for rank in range(W):
+        assert_attention_close(outs[rank], ref[rank], f"causal {U}x{R} rank {rank}")
+    assert_attention_close(torch.cat(outs, dim=-2), whole, f"causal {U}x{R} whole sequence")
+    # non-causal calls in between keep working on the same buffers and counters
+    plain = cluster.attention(qs, ks, vs)
+    again = cluster.attention(qs, ks, vs, is_causal=True)
+    for rank in range(W):
+        assert torch.equal(again[rank], outs[rank]) and not torch.equal(plain[rank], outs[rank])
+
+
 @pytest.mark.parametrize("name,U,R", [("ulysses_short_kv", 2, 1), ("ring_short_kv", 1, 2)])
 def test_world2_short_kv_against_reference_outputs(golden_dir, name, U, R):
     g = np.load(golden_dir / "cp_attention_w2.npz")
@@ -143,6 +175,10 @@ def _mp_worker(rank, world, port, mode, ret):
             out = pa.ulysses_attn_func(qs, ks, vs)
         elif mode == "ring":
             out = pa.ring_attn_func(qs, ks, vs)
+        elif mode == "ring_causal":
+            out = pa.ring_attn_func(qs, ks, vs, is_causal=True)
+        elif mode == "ulysses_causal":
+            out = pa.ulysses_attn_func(qs, ks, vs, is_causal=True)
         else:
             mesh = dist.init_device_mesh("cuda", (world // 2, 2), mesh_dim_names=("ring", "ulysses")) if rep == 0 else mesh
             with pa.UnifiedAttnMode(mesh):
@@ -159,7 +195,7 @@ def _mp_worker(rank, world, port, mode, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["ulysses", "ring", "unified"])
+@pytest.mark.parametrize("mode", ["ulysses", "ring", "unified", "ring_causal", "ulysses_causal"])
 def test_multi_gpu_processes(mode):
     n = torch.cuda.device_count()
     if n < 2:
@@ -171,7 +207,7 @@ def test_multi_gpu_processes(mode):
 
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
-    port = 29700 + {"ulysses": 1, "ring": 2, "unified": 3}[mode]
+    port = 29700 + {"ulysses": 1, "ring": 2, "unified": 3, "ring_causal": 4, "ulysses_causal": 5}[mode]
     procs = [ctx.Process(target=_mp_worker, args=(r, world, port, mode, ret)) for r in range(world)]
     for p in procs:
         p.start()
@@ -181,5 +217,6 @@ def test_multi_gpu_processes(mode):
     assert same, "repeated calls gave different results"
     H, S = 4, world * 515
     q, k, v = seeded_qkv(1, H, S, S, seed=21, device="cpu")
-    ref, _ = O.sdpa_with_lse(q.float().numpy(), k.float().numpy(), v.float().numpy())
+    ref, _ = O.sdpa_with_lse(q.float().numpy(), k.float().numpy(), v.float().numpy(),
+                             is_causal=mode.endswith("causal"))
     assert_attention_close(torch.from_numpy(full), ref, f"{mode} world {world}")
