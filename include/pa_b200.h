@@ -53,7 +53,7 @@ int pa_version(void);
  * Tensors are [batch, heads, seq, head_dim] with arbitrary element strides for the first
  * three dims and stride 1 for head_dim (BSHD memory viewed as BHSD is fine). Base pointers
  * and byte strides of q, k, v must be multiples of 16 bytes; out needs 16-byte alignment of
- * base and strides too. head_dim must be 128; dtype bf16 or f16; accumulation is fp32.
+ * base and strides too. head_dim must be 64 or 128; dtype bf16 or f16; accumulation is fp32.
  * lse may be NULL. status may be NULL; if given it must point to a zero-initialised device
  * int that receives a pa_device_status code when a wait inside the kernel gives up.
  * ---------------------------------------------------------------------------------------- */
@@ -95,8 +95,8 @@ int pa_attn_fwd(const pa_attn_args* args, void* stream);
 struct pa_cp_push_args;
 
 typedef struct pa_cp_attn_args {
-    const void* q_stage;     /* [n_q_chunks, batch, heads, q_rows, 128] */
-    const void* k_stage;     /* [n_kv_chunks, batch, heads, kv_rows, 128] */
+    const void* q_stage;     /* [n_q_chunks, batch, heads, q_rows, head_dim] */
+    const void* k_stage;     /* [n_kv_chunks, batch, heads, kv_rows, head_dim] */
     const void* v_stage;
     int32_t batch, heads, head_dim, dtype;
     int32_t n_q_chunks, q_rows, q_first;
@@ -121,7 +121,7 @@ typedef struct pa_cp_attn_args {
     const struct pa_cp_push_args* fused_push;
     /* Zero-copy own shard (each may be NULL): when given, query chunk q_first (key/value chunk
      * kv_first) is not read from the staging buffer but straight from this rank's own tensor,
-     * [batch, all heads, rows, 128] with the given element strides, heads
+     * [batch, all heads, rows, head_dim] with the given element strides, heads
      * [local_head_offset, local_head_offset + heads); its ready flag is ignored. */
     const void* q_local;
     const void* k_local;
@@ -162,7 +162,7 @@ int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps,
  * Exchange. Replaces the NCCL all_to_all_single calls of _sdpa_input_all_to_all /
  * _sdpa_output_all_to_all (src/para_attn/para_attn_interface.py:52-87, through
  * src/para_attn/primitives.py:72-78) and the K/V rotation of torch:_AllToAllRotater
- * (torch:247-263): each job copies rows [batch, head0..head0+heads, rows, 128] of a local
+ * (torch:247-263): each job copies rows [batch, head0..head0+heads, rows, head_dim] of a local
  * tensor to dst (normally a peer GPU's mapped staging buffer) with the given element
  * strides; when all jobs of a destination are stored, flag[dest] on that destination is
  * increased by ctas_per_dest in total (each CTA adds 1 with a system-scope release).
@@ -176,11 +176,11 @@ int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps,
 typedef struct pa_push_job {
     const void* src;
     void* dst;
-    int64_t src_stride[3];   /* element strides (batch, head, row); 128 contiguous 16-bit elements per row */
+    int64_t src_stride[3];   /* element strides (batch, head, row); head_dim contiguous 16-bit elements per row */
     int64_t dst_stride[3];
     int32_t head0, heads, batch, rows;
     int32_t dest;            /* index into pa_cp_push_args.flag */
-    int32_t pad_;
+    int32_t head_dim;        /* 64 or 128; 0 means 128 */
 } pa_push_job;
 
 typedef struct pa_cp_push_args {

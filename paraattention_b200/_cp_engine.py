@@ -220,6 +220,7 @@ def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int,
         j.dst_stride[0], j.dst_stride[1], j.dst_stride[2] = js.heads * n_rows * D, n_rows * D, D
         j.head0, j.heads, j.batch, j.rows = js.head0, js.heads, B, n_rows
         j.dest = js.dest
+        j.head_dim = D
     pa.n_jobs = len(jobs)
     pa.n_dest = plan.world
     for d in range(plan.world):
@@ -378,7 +379,7 @@ class CpEngine:
 
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float],
                   is_causal: bool = False) -> torch.Tensor:
-        """q: [B, H, s_q, 128], k/v: [B, H, s_kv, 128] local shards -> [B, H, s_q, 128] local output.
+        """q: [B, H, s_q, D], k/v: [B, H, s_kv, D] local shards -> [B, H, s_q, D] local output.
         ``is_causal`` masks over the whole sequence, shards taken in flat-rank order."""
         B, H, sq, D = q.shape
         skv = k.shape[2]
@@ -410,7 +411,7 @@ class CpEngine:
         out_local = None
         if self.ulysses == 1:
             out_local = torch.empty((B, sq, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
-        key = (B, H, sq, skv, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(), is_causal)
+        key = (B, H, sq, skv, D, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(), is_causal)
         ent = self._launch_cache.get(key)
         if ent is None:
             push = build_push_args(plan, ws, par, q, k, v, n_push)

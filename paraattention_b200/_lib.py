@@ -72,7 +72,7 @@ class PushJob(C.Structure):
         ("src", C.c_void_p), ("dst", C.c_void_p),
         ("src_stride", C.c_int64 * 3), ("dst_stride", C.c_int64 * 3),
         ("head0", C.c_int32), ("heads", C.c_int32), ("batch", C.c_int32), ("rows", C.c_int32),
-        ("dest", C.c_int32), ("pad_", C.c_int32),
+        ("dest", C.c_int32), ("head_dim", C.c_int32),
     ]
 
 

@@ -34,7 +34,8 @@
 
 namespace pa {
 
-constexpr int kHeadDim = 128;
+// head_dim is a template parameter of the kernel (kD = 64 or 128). Shared-memory slots keep
+// the 128-wide size for both: a 64-wide tile is one swizzle atom and fills the first half.
 constexpr int kTileM = 128;
 constexpr int kTileN = 128;
 constexpr int kHalfBytes = 128 * 128;       // 128 rows x 64 elements x 2 B (one swizzle atom wide)
@@ -134,12 +135,16 @@ __device__ __forceinline__ void pair_sync(int id) {
     asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
 }
 
-template <bool kBF16, bool kDebug, bool kCausal>
+template <bool kBF16, bool kDebug, bool kCausal, int kD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ql,
                 const __grid_constant__ CUtensorMap tm_kl, const __grid_constant__ CUtensorMap tm_vl,
                 const __grid_constant__ AttnParams p, const __grid_constant__ PushParams push) {
+    static_assert(kD == 64 || kD == 128, "head_dim 64 or 128");
+    static_assert(!kDebug || kD == 128, "the debug hooks exist for head_dim 128 only");
+    constexpr int kAtoms = kD / 64;                    // 64-element swizzle atoms per row
+    constexpr int kOperandBytes = kAtoms * kHalfBytes; // bytes one Q / K / V tile occupies
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -259,11 +264,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const CUtensorMap* mq = q_in_place ? &tm_ql : &tm_q;
                 const int hq = q_in_place ? head + p.local_head0 : head;
                 const int cq = q_in_place ? 0 : qc;
-                mbar_expect_tx(bq, 2 * kTileBytes);
+                mbar_expect_tx(bq, 2 * kOperandBytes);
 #pragma unroll
                 for (int t = 0; t < 2; ++t)
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
+                    for (int h = 0; h < kAtoms; ++h)
                         tma_load_5d(sQ + t * kTileBytes + h * kHalfBytes, mq, bq, h * 64,
                                     row0 + t * kTileM, hq, bidx, cq);
             }
@@ -294,9 +299,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                        pipe_limit, PA_DEV_TIMEOUT_PIPE);
                         if (!ok) break;
                     }
-                    mbar_expect_tx(bk, kTileBytes);
+                    mbar_expect_tx(bk, kOperandBytes);
                     tma_load_5d(sK + st * kTileBytes, mk, bk, 0, t * kTileN, hk, bidx, ck);
-                    tma_load_5d(sK + st * kTileBytes + kHalfBytes, mk, bk, 64, t * kTileN, hk, bidx, ck);
+                    if (kAtoms == 2)
+                        tma_load_5d(sK + st * kTileBytes + kHalfBytes, mk, bk, 64, t * kTileN, hk, bidx, ck);
                     if (j >= kStages) {
                         ok = mbar_wait(smem_u32(&ctl->v_empty[st]), ph ^ 1, s_abort, p.status,
                                        pipe_limit, PA_DEV_TIMEOUT_PIPE);
@@ -305,9 +311,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                             break;
                         }
                     }
-                    mbar_expect_tx(bv, kTileBytes);
+                    mbar_expect_tx(bv, kOperandBytes);
                     tma_load_5d(sV + st * kTileBytes, mv, bv, 0, t * kTileN, hk, bidx, ck);
-                    tma_load_5d(sV + st * kTileBytes + kHalfBytes, mv, bv, 64, t * kTileN, hk, bidx, ck);
+                    if (kAtoms == 2)
+                        tma_load_5d(sV + st * kTileBytes + kHalfBytes, mv, bv, 64, t * kTileN, hk, bidx, ck);
                     issued = j + 1;
                 }
             }
@@ -330,7 +337,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // k-step loops are unrolled and every descriptor is a base plus a constant.
         if (lane == 0 && n_tiles > 0) {
             constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN);
-            constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kHeadDim);
+            constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kD);
             constexpr uint32_t idesc_pv64 = make_idesc_f16(kBF16, true, kTileM, 64);
             const uint32_t v_lbo = kDebug ? static_cast<uint32_t>(p.v_lbo) : kHalfBytes;
             const uint32_t v_sbo = kDebug ? static_cast<uint32_t>(p.v_sbo) : 1024u;
@@ -346,7 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const uint64_t b0 = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
                 const uint32_t d = tmem + kColS0 + t * kTileN;
 #pragma unroll
-                for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+                for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
                     tc_mma_ss(d, a0 + off, b0 + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
@@ -355,7 +362,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             auto issue_pv_half = [&](int t, int st, int half, bool acc) {
                 const uint64_t b0 = dv0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
                 const uint32_t a0 = tmem + kColS0 + t * kTileN;
-                const uint32_t d = tmem + kColO0 + t * kHeadDim;
+                const uint32_t d = tmem + kColO0 + t * kD;
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
                     const int ks = half * 4 + k4;
@@ -438,7 +445,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN + half * 64;  // my 64 logit columns
-        const uint32_t tO = tmem + lane_base + kColO0 + t * kHeadDim + half * 64;  // my 64 output columns
+        const uint32_t tO = tmem + lane_base + kColO0 + t * kD + half * (kD / 2);  // my half of the output columns
         const uint32_t bs = smem_u32(&ctl->s_full[t]);
         const uint32_t bp = smem_u32(&ctl->p_full[t][half]);
         const uint32_t bo = smem_u32(&ctl->o_done[t]);
@@ -517,7 +524,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                        PA_DEV_TIMEOUT_PIPE) && ok;
                         tc_fence_after();
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) {
+                        for (int c = 0; c < kAtoms; ++c) {
                             uint32_t o[32];
                             tmem_ld32(tO + c * 32, o);
                             tc_wait_ld();
@@ -601,9 +608,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float inv = empty ? 0.0f : 1.0f / l_row;
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
                              (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
-                              static_cast<long long>(row) * p.o_ss) + half * 64;
+                              static_cast<long long>(row) * p.o_ss) + half * (kD / 2);
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            for (int c = 0; c < kAtoms; ++c) {
                 uint32_t o[32];
                 tmem_ld32(tO + c * 32, o);
                 tc_wait_ld();

@@ -36,15 +36,17 @@ __device__ __forceinline__ void push_row_ptrs(const pa_push_job& job, long long 
 
 // All threads of the calling CTA copy this CTA's share (CTA `cta` of `n_ctas`) of every job
 // bound for `dest`, then one thread publishes the arrival with a system-scope release.
-// A row is 128 x 16-bit = 256 B = 16 lanes x 16 B. Must be called by the whole CTA.
+// A row of head_dim 128 is 256 B = 16 lanes x 16 B, one of head_dim 64 is 8 lanes. Must be
+// called by the whole CTA.
 __device__ __forceinline__ void push_to_dest(const PushParams& p, int dest, int cta, int n_ctas) {
-    const int lane16 = threadIdx.x & 15;
-    const int sub = threadIdx.x >> 4;
-    const int rows_per_cta = blockDim.x >> 4;
-    const long long step = static_cast<long long>(n_ctas) * rows_per_cta;
     for (int j = 0; j < p.n_jobs; ++j) {
         const pa_push_job& job = p.jobs[j];
         if (job.dest != dest) continue;
+        const int lane_bits = (job.head_dim == 64) ? 3 : 4;
+        const int lane16 = threadIdx.x & ((1 << lane_bits) - 1);
+        const int sub = threadIdx.x >> lane_bits;
+        const int rows_per_cta = blockDim.x >> lane_bits;
+        const long long step = static_cast<long long>(n_ctas) * rows_per_cta;
         const long long total = static_cast<long long>(job.batch) * job.heads * job.rows;
         for (long long r0 = static_cast<long long>(cta) * rows_per_cta + sub; r0 < total; r0 += step * kPushUnroll) {
             uint4 val[kPushUnroll];

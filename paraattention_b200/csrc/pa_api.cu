@@ -45,15 +45,15 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// 5-D map over [chunk][batch][head][row][128] with element strides (head_dim stride 1); the box is
+// 5-D map over [chunk][batch][head][row][head_dim] with element strides (head_dim stride 1); the box is
 // 64 elements x 128 rows with the 128-byte swizzle the MMA descriptors expect.
-int make_map(CUtensorMap* map, const void* base, int dtype, int rows, int heads, int batch, int chunks,
+int make_map(CUtensorMap* map, const void* base, int dtype, int head_dim, int rows, int heads, int batch, int chunks,
              int64_t s_row, int64_t s_head, int64_t s_batch, int64_t s_chunk, const char* what) {
     EncodeTiledFn enc = get_encode_fn();
     if (enc == nullptr) return fail(PA_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
     if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
         return fail(PA_EINVAL, "%s: base pointer must be 16-byte aligned", what);
-    cuuint64_t dims[5] = {128, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads),
+    cuuint64_t dims[5] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads),
                           static_cast<cuuint64_t>(batch), static_cast<cuuint64_t>(chunks)};
     int64_t es[4] = {s_row, s_head, s_batch, s_chunk};
     cuuint64_t strides[4];
@@ -75,10 +75,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int rows, int heads,
     return PA_OK;
 }
 
-template <bool kBF16, bool kDebug, bool kCausal>
+template <bool kBF16, bool kDebug, bool kCausal, int kD>
 int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream) {
-    auto kern = pa::attn_fwd_kernel<kBF16, kDebug, kCausal>;
+    auto kern = pa::attn_fwd_kernel<kBF16, kDebug, kCausal, kD>;
     static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
     {
@@ -99,16 +99,19 @@ int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa:
 
 template <bool kBF16, bool kDebug>
 int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
-                cudaStream_t stream) {
-    if (p.causal) {
-        if (kDebug) return fail(PA_ENOTSUP, "the debug hooks are built without causal masking");
-        return launch_attn_inst<kBF16, false, true>(maps, p, push, grid, stream);
+                cudaStream_t stream, int head_dim) {
+    if (kDebug && (p.causal || head_dim != 128))
+        return fail(PA_ENOTSUP, "the debug hooks are built for non-causal head_dim 128 only");
+    if (head_dim == 64) {
+        return p.causal ? launch_attn_inst<kBF16, false, true, 64>(maps, p, push, grid, stream)
+                        : launch_attn_inst<kBF16, false, false, 64>(maps, p, push, grid, stream);
     }
-    return launch_attn_inst<kBF16, kDebug, false>(maps, p, push, grid, stream);
+    if (p.causal) return launch_attn_inst<kBF16, false, true, 128>(maps, p, push, grid, stream);
+    return launch_attn_inst<kBF16, kDebug, false, 128>(maps, p, push, grid, stream);
 }
 
 int check_common(int head_dim, int dtype, float scale) {
-    if (head_dim != 128) return fail(PA_ENOTSUP, "head_dim %d: only 128 is built", head_dim);
+    if (head_dim != 128 && head_dim != 64) return fail(PA_ENOTSUP, "head_dim %d: only 64 and 128 are built", head_dim);
     if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "dtype %d: expected PA_BF16 or PA_F16", dtype);
     if (!(scale > 0.f) || !std::isfinite(scale)) return fail(PA_EINVAL, "scale must be positive and finite");
     return PA_OK;
@@ -134,11 +137,11 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
 
     CUtensorMap maps[6];
     CUtensorMap &mq = maps[0], &mk = maps[1], &mv = maps[2];
-    rc = make_map(&mq, a->q, a->dtype, a->seq_q, a->heads, a->batch, 1, a->q_stride[2], a->q_stride[1], a->q_stride[0], 0, "q");
+    rc = make_map(&mq, a->q, a->dtype, a->head_dim, a->seq_q, a->heads, a->batch, 1, a->q_stride[2], a->q_stride[1], a->q_stride[0], 0, "q");
     if (rc != PA_OK) return rc;
-    rc = make_map(&mk, a->k, a->dtype, a->seq_kv, a->heads, a->batch, 1, a->k_stride[2], a->k_stride[1], a->k_stride[0], 0, "k");
+    rc = make_map(&mk, a->k, a->dtype, a->head_dim, a->seq_kv, a->heads, a->batch, 1, a->k_stride[2], a->k_stride[1], a->k_stride[0], 0, "k");
     if (rc != PA_OK) return rc;
-    rc = make_map(&mv, a->v, a->dtype, a->seq_kv, a->heads, a->batch, 1, a->v_stride[2], a->v_stride[1], a->v_stride[0], 0, "v");
+    rc = make_map(&mv, a->v, a->dtype, a->head_dim, a->seq_kv, a->heads, a->batch, 1, a->v_stride[2], a->v_stride[1], a->v_stride[0], 0, "v");
     if (rc != PA_OK) return rc;
 
     maps[3] = mq;
@@ -180,11 +183,11 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     pa::PushParams push;
     memset(&push, 0, sizeof(push));
     if (debug) {
-        return a->dtype == PA_BF16 ? launch_attn<true, true>(maps, p, push, int(grid), s)
-                                   : launch_attn<false, true>(maps, p, push, int(grid), s);
+        return a->dtype == PA_BF16 ? launch_attn<true, true>(maps, p, push, int(grid), s, a->head_dim)
+                                   : launch_attn<false, true>(maps, p, push, int(grid), s, a->head_dim);
     }
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s)
-                               : launch_attn<false, false>(maps, p, push, int(grid), s);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s, a->head_dim)
+                               : launch_attn<false, false>(maps, p, push, int(grid), s, a->head_dim);
 }
 
 int fill_push(const pa_cp_push_args* a, pa::PushParams* p) {
@@ -199,6 +202,8 @@ int fill_push(const pa_cp_push_args* a, pa::PushParams* p) {
         if (job.dest < 0 || job.dest >= a->n_dest) return fail(PA_EINVAL, "job %d: dest out of range", j);
         if (job.batch <= 0 || job.heads <= 0 || job.rows <= 0 || job.head0 < 0)
             return fail(PA_EINVAL, "job %d: batch, heads, rows must be positive", j);
+        if (job.head_dim != 0 && job.head_dim != 64 && job.head_dim != 128)
+            return fail(PA_EINVAL, "job %d: head_dim must be 64 or 128 (0 = 128)", j);
         if ((reinterpret_cast<uintptr_t>(job.src) & 15u) || (reinterpret_cast<uintptr_t>(job.dst) & 15u))
             return fail(PA_EINVAL, "job %d: src and dst must be 16-byte aligned", j);
         for (int i = 0; i < 3; ++i)
@@ -250,13 +255,14 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     }
     CUtensorMap maps[6];
     CUtensorMap &mq = maps[0], &mk = maps[1], &mv = maps[2];
-    const int64_t qs_h = int64_t(a->q_rows) * 128, qs_b = qs_h * a->heads, qs_c = qs_b * a->batch;
-    const int64_t ks_h = int64_t(a->kv_rows) * 128, ks_b = ks_h * a->heads, ks_c = ks_b * a->batch;
-    rc = make_map(&mq, a->q_stage, a->dtype, a->q_rows, a->heads, a->batch, a->n_q_chunks, 128, qs_h, qs_b, qs_c, "q_stage");
+    const int64_t D = a->head_dim;
+    const int64_t qs_h = int64_t(a->q_rows) * D, qs_b = qs_h * a->heads, qs_c = qs_b * a->batch;
+    const int64_t ks_h = int64_t(a->kv_rows) * D, ks_b = ks_h * a->heads, ks_c = ks_b * a->batch;
+    rc = make_map(&mq, a->q_stage, a->dtype, a->head_dim, a->q_rows, a->heads, a->batch, a->n_q_chunks, D, qs_h, qs_b, qs_c, "q_stage");
     if (rc != PA_OK) return rc;
-    rc = make_map(&mk, a->k_stage, a->dtype, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, 128, ks_h, ks_b, ks_c, "k_stage");
+    rc = make_map(&mk, a->k_stage, a->dtype, a->head_dim, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, D, ks_h, ks_b, ks_c, "k_stage");
     if (rc != PA_OK) return rc;
-    rc = make_map(&mv, a->v_stage, a->dtype, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, 128, ks_h, ks_b, ks_c, "v_stage");
+    rc = make_map(&mv, a->v_stage, a->dtype, a->head_dim, a->kv_rows, a->heads, a->batch, a->n_kv_chunks, D, ks_h, ks_b, ks_c, "v_stage");
     if (rc != PA_OK) return rc;
 
     maps[3] = mq;
@@ -272,17 +278,17 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         p.local_head0 = a->local_head_offset;
     }
     if (a->q_local != nullptr) {
-        rc = make_map(&maps[3], a->q_local, a->dtype, a->q_rows, a->local_total_heads, a->batch, 1, a->q_local_stride[2],
+        rc = make_map(&maps[3], a->q_local, a->dtype, a->head_dim, a->q_rows, a->local_total_heads, a->batch, 1, a->q_local_stride[2],
                       a->q_local_stride[1], a->q_local_stride[0], 0, "q_local");
         if (rc != PA_OK) return rc;
         p.q_local_chunk = a->q_first;
     }
     if (a->k_local != nullptr || a->v_local != nullptr) {
         if (a->k_local == nullptr || a->v_local == nullptr) return fail(PA_EINVAL, "k_local and v_local go together");
-        rc = make_map(&maps[4], a->k_local, a->dtype, a->kv_rows, a->local_total_heads, a->batch, 1, a->k_local_stride[2],
+        rc = make_map(&maps[4], a->k_local, a->dtype, a->head_dim, a->kv_rows, a->local_total_heads, a->batch, 1, a->k_local_stride[2],
                       a->k_local_stride[1], a->k_local_stride[0], 0, "k_local");
         if (rc != PA_OK) return rc;
-        rc = make_map(&maps[5], a->v_local, a->dtype, a->kv_rows, a->local_total_heads, a->batch, 1, a->v_local_stride[2],
+        rc = make_map(&maps[5], a->v_local, a->dtype, a->head_dim, a->kv_rows, a->local_total_heads, a->batch, 1, a->v_local_stride[2],
                       a->v_local_stride[1], a->v_local_stride[0], 0, "v_local");
         if (rc != PA_OK) return rc;
         p.kv_local_chunk = a->kv_first;
@@ -340,8 +346,8 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         push.n_push_ctas = n;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s)
-                               : launch_attn<false, false>(maps, p, push, int(grid), s);
+    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s, a->head_dim)
+                               : launch_attn<false, false>(maps, p, push, int(grid), s, a->head_dim);
 }
 
 int pa_cp_push(const pa_cp_push_args* a, void* stream) {

@@ -36,8 +36,9 @@ def _check_inputs(query, key, value, attn_mask, dropout_p, is_causal):
         raise NotImplementedError("attn_mask is not built into the sm_100a attention kernel")
     if dropout_p != 0.0:
         raise NotImplementedError("dropout_p must be 0: the library is forward/inference only")
-    if query.shape[-1] != 128 or key.shape[-1] != 128 or value.shape[-1] != 128:
-        raise NotImplementedError(f"head_dim {query.shape[-1]}: only 128 is built")
+    D = query.shape[-1]
+    if D not in (64, 128) or key.shape[-1] != D or value.shape[-1] != D:
+        raise NotImplementedError(f"head_dim {D}: only 64 and 128 are built (query, key and value alike)")
     assert key.shape[:2] == query.shape[:2] and value.shape == key.shape, "mismatched batch/head/key shapes"
 
 

@@ -40,8 +40,9 @@ def _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal) -> bool:
         and key.dtype == query.dtype
         and value.dtype == query.dtype
         and query.ndim == 4
-        and query.shape[-1] == 128
-        and value.shape[-1] == 128
+        and query.shape[-1] in (64, 128)
+        and key.shape[-1] == query.shape[-1]
+        and value.shape[-1] == query.shape[-1]
         and attn_mask is None
         and dropout_p == 0.0
     )
@@ -68,7 +69,7 @@ def _cp_attention(query, key, value, scale, *, flat_group, ulysses, ring, u, r, 
 def _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, what):
     if not _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal):
         raise NotImplementedError(
-            f"{what}: the context-parallel kernel is built for CUDA bf16/f16 tensors with head_dim 128, "
+            f"{what}: the context-parallel kernel is built for CUDA bf16/f16 tensors with head_dim 64 or 128, "
             "no mask, no dropout")
 
 

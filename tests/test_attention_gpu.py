@@ -78,6 +78,31 @@ def test_abi_causal_attention_matches_oracle(B, H, Sq, Skv, dtype):
     assert torch.equal(out[:, :, 0], v[:, :, 0])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,H,Sq,Skv", [(1, 1, 128, 128), (1, 2, 127, 129), (2, 3, 515, 1000), (1, 4, 4096, 1024),
+                                        (1, 2, 4095, 4095)])
+def test_abi_head_dim_64_matches_oracle(B, H, Sq, Skv, causal, dtype):
+    """head_dim 64, the width of the reference's own test matrix (tests/test_interface.py:130-140:
+    S_Q 4096, S_KV 4096 or 1024, fp16 and bf16, causal only where S_Q == S_KV)."""
+    if causal and Sq != Skv and Sq > 1000:
+        pytest.skip("the reference skips causal runs with different lengths")
+    q, k, v = seeded_qkv(B, H, Sq, Skv, D=64, seed=Sq * 13 + Skv, dtype=dtype)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc, out, lse = _abi_attention(q, k, v, status=status, is_causal=causal)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref_out, ref_lse = O.sdpa_with_lse(*(t.float().cpu().numpy() for t in (q, k, v)), is_causal=causal)
+    assert_attention_close(out, ref_out, f"D64 causal={causal} B{B} H{H} Sq{Sq} Skv{Skv}")
+    assert_lse_close(lse, ref_lse)
+    # strided [B, S, H, D] views through the custom op
+    from paraattention_b200 import ops
+
+    qb, kb, vb = (t.transpose(1, 2).contiguous().transpose(1, 2) for t in (q, k, v))
+    assert torch.equal(ops.attention_forward(qb, kb, vb, is_causal=causal), out)
+
+
 @pytest.mark.parametrize("B,H,Sq,Skv", SHAPES)
 def test_abi_attention_matches_oracle(B, H, Sq, Skv):
     q, k, v = seeded_qkv(B, H, Sq, Skv, seed=Sq * 7 + Skv)
@@ -127,9 +152,9 @@ def test_abi_rejects_bad_arguments():
     a = L.AttnArgs()
     assert lib.pa_attn_fwd(C.byref(a), None) == L.PA_EINVAL
     assert b"non-NULL" in lib.pa_last_error()
-    q64 = torch.zeros(1, 1, 128, 64, dtype=torch.bfloat16, device="cuda")
-    rc, _, _ = _abi_attention(q64, q64, q64)
-    assert rc == L.PA_ENOTSUP
+    q96 = torch.zeros(1, 1, 128, 96, dtype=torch.bfloat16, device="cuda")
+    rc, _, _ = _abi_attention(q96, q96, q96)
+    assert rc == L.PA_ENOTSUP and b"head_dim 96" in lib.pa_last_error()
     buf = torch.zeros(128 * 128 + 8, dtype=torch.bfloat16, device="cuda")
     rc, _, _ = _abi_attention(buf[3:3 + 127 * 128].view(1, 1, 127, 128), k, v)
     assert rc == L.PA_EINVAL  # base pointer not 16-byte aligned

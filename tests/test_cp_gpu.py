@@ -65,6 +65,19 @@ def test_world8_meshes_causal_against_oracle(U, R, H, S):
         assert torch.equal(again[rank], outs[rank]) and not torch.equal(plain[rank], outs[rank])
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("U,R,H,S", [(2, 1, 4, 2 * 515), (1, 2, 2, 2 * 300), (2, 2, 4, 4 * 257), (4, 2, 8, 8 * 131)])
+def test_head_dim_64_meshes_against_oracle(U, R, H, S, causal):
+    W = U * R
+    q, k, v = seeded_qkv(1, H, S, S, D=64, seed=U * 10 + R + 200)
+    qs, ks, vs = ([t.contiguous() for t in x.chunk(W, dim=-2)] for x in (q, k, v))
+    outs = LocalCluster(U, R).attention(qs, ks, vs, is_causal=causal)
+    ref = O.unified_attention([t.float().cpu().numpy() for t in qs], [t.float().cpu().numpy() for t in ks],
+                              [t.float().cpu().numpy() for t in vs], ulysses=U, ring=R, is_causal=causal)
+    for rank in range(W):
+        assert_attention_close(outs[rank], ref[rank], f"D64 causal={causal} {U}x{R} rank {rank}")
+
+
 @pytest.mark.parametrize("name,U,R", [("ulysses_short_kv", 2, 1), ("ring_short_kv", 1, 2)])
 def test_world2_short_kv_against_reference_outputs(golden_dir, name, U, R):
     g = np.load(golden_dir / "cp_attention_w2.npz")
@@ -167,7 +180,7 @@ def _mp_worker(rank, world, port, mode, ret):
     import paraattention_b200 as pa
 
     H, S = 4, world * 515
-    q, k, v = seeded_qkv(1, H, S, S, seed=21, device="cpu")
+    q, k, v = seeded_qkv(1, H, S, S, D=64 if "d64" in mode else 128, seed=21, device="cpu")
     qs, ks, vs = (x.chunk(world, dim=-2)[rank].cuda() for x in (q, k, v))
     results = {}
     for rep in range(3):
@@ -179,6 +192,12 @@ def _mp_worker(rank, world, port, mode, ret):
             out = pa.ring_attn_func(qs, ks, vs, is_causal=True)
         elif mode == "ulysses_causal":
             out = pa.ulysses_attn_func(qs, ks, vs, is_causal=True)
+        elif mode == "ring_d64_causal":
+            with pa.RingAttnMode():
+                out = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True)
+        elif mode == "ulysses_d64":
+            with pa.UlyssesAttnMode():
+                out = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs)
         else:
             mesh = dist.init_device_mesh("cuda", (world // 2, 2), mesh_dim_names=("ring", "ulysses")) if rep == 0 else mesh
             with pa.UnifiedAttnMode(mesh):
@@ -195,7 +214,8 @@ def _mp_worker(rank, world, port, mode, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["ulysses", "ring", "unified", "ring_causal", "ulysses_causal"])
+@pytest.mark.parametrize("mode", ["ulysses", "ring", "unified", "ring_causal", "ulysses_causal", "ring_d64_causal",
+                                  "ulysses_d64"])
 def test_multi_gpu_processes(mode):
     n = torch.cuda.device_count()
     if n < 2:
@@ -207,7 +227,8 @@ def test_multi_gpu_processes(mode):
 
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
-    port = 29700 + {"ulysses": 1, "ring": 2, "unified": 3, "ring_causal": 4, "ulysses_causal": 5}[mode]
+    port = 29700 + {"ulysses": 1, "ring": 2, "unified": 3, "ring_causal": 4, "ulysses_causal": 5, "ring_d64_causal": 6,
+                    "ulysses_d64": 7}[mode]
     procs = [ctx.Process(target=_mp_worker, args=(r, world, port, mode, ret)) for r in range(world)]
     for p in procs:
         p.start()
@@ -216,7 +237,7 @@ def test_multi_gpu_processes(mode):
         p.join(timeout=60)
     assert same, "repeated calls gave different results"
     H, S = 4, world * 515
-    q, k, v = seeded_qkv(1, H, S, S, seed=21, device="cpu")
+    q, k, v = seeded_qkv(1, H, S, S, D=64 if "d64" in mode else 128, seed=21, device="cpu")
     ref, _ = O.sdpa_with_lse(q.float().numpy(), k.float().numpy(), v.float().numpy(),
                              is_causal=mode.endswith("causal"))
     assert_attention_close(torch.from_numpy(full), ref, f"{mode} world {world}")
