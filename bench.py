@@ -47,17 +47,26 @@ def parse_args():
                     help="attention = the headline op benchmark; the others time one transformer forward")
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the block count (quick runs)")
     ap.add_argument("--fbcache", type=float, default=0.0, help="DiT workloads: First-Block-Cache threshold (0 = off)")
+    ap.add_argument("--causal", action="store_true", help="attention workload: causal mask (FLOPs counted as half)")
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128], help="attention workload: head_dim")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
 
 
+VARIANT = {"D": 128, "causal": False}  # set from --head-dim / --causal; the headline row is D=128 non-causal
+
+
 def workload_name(H, S):
-    return f"attention-op sweep row: bf16 non-causal B=1 H={H} S={S} D=128"
+    kind = "causal" if VARIANT["causal"] else "non-causal"
+    return f"attention-op sweep row: bf16 {kind} B=1 H={H} S={S} D={VARIANT['D']}"
 
 
-def attention_flops(H, S, B=1, D=128):
-    return 4.0 * B * H * S * S * D
+def attention_flops(H, S, B=1):
+    """4*B*H*S^2*D for the two GEMMs; a causal run is counted as half of that (the visible
+    triangle), the usual convention."""
+    f = 4.0 * B * H * S * S * VARIANT["D"]
+    return f / 2 if VARIANT["causal"] else f
 
 
 def load_peaks():
@@ -76,7 +85,7 @@ def make_inputs(H, S, seed=0):
     outs = []
     for i in range(3):
         g = torch.Generator().manual_seed(seed + i)
-        x = torch.randn(1, H, S, 128, generator=g) * 0.5
+        x = torch.randn(1, H, S, VARIANT["D"], generator=g) * 0.5
         if i < 2:
             x = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)
         outs.append(x.to(torch.bfloat16))
@@ -226,6 +235,7 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()  # early: nvidia-smi needs a moment before its first sample
+    causal = VARIANT["causal"]
     q_h, k_h, v_h = make_inputs(H, S_pad)
     if world > 1:
         q_h, k_h, v_h = (x.chunk(world, dim=-2)[rank].contiguous() for x in (q_h, k_h, v_h))
@@ -235,14 +245,14 @@ def run_ours(args):
 
     if world == 1:
         def step(qq, kk, vv):
-            return ops.attention_forward(qq, kk, vv)
+            return ops.attention_forward(qq, kk, vv, is_causal=causal)
         launches_per_step = 1
     else:
         mode = pa.UnifiedAttnMode(mesh)
 
         def step(qq, kk, vv):
             with mode:
-                return torch.nn.functional.scaled_dot_product_attention(qq, kk, vv)
+                return torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=causal)
         launches_per_step = 2 + (1 if U > 1 else 0)  # push + attention (+ output-arrival wait)
 
     def sync_all():
@@ -286,7 +296,7 @@ def run_ours(args):
     # end to end through the public API with host buffers: H2D of q, k, v and D2H of the result
     e2e = None
     if not args.no_e2e:
-        out_h = torch.empty((1, q_h.shape[2], H, 128), dtype=torch.bfloat16).pin_memory()
+        out_h = torch.empty((1, q_h.shape[2], H, VARIANT["D"]), dtype=torch.bfloat16).pin_memory()
 
         def e2e_step():
             qq, kk, vv = q_h.to(dev, non_blocking=True), k_h.to(dev, non_blocking=True), v_h.to(dev, non_blocking=True)
@@ -308,14 +318,14 @@ def run_ours(args):
     per_gpu_tflops = value / world
     if world == 1:
         roofline = {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": per_gpu_tflops / peaks["bf16_tflops"], "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((H, S)),
+                    "frac": per_gpu_tflops / peaks["bf16_tflops"], "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((H, S)) if (VARIANT["D"] == 128 and not causal) else None,
                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "kernel": "attn_fwd_kernel",
                     "flops_per_launch": flops}
     else:
         # slower of tensor time and NVLink time (770 GB/s measured per direction per GPU)
         hl = H // U
         s_loc = S_pad // world
-        sent = (world - 1) * 2 * hl * s_loc * 128 * 2 + (U - 1) * 2 * hl * s_loc * 128 * 2  # K,V to all; Q out + O back
+        sent = ((world - 1) * 2 + (U - 1) * 2) * hl * s_loc * VARIANT["D"] * 2  # K,V to all; Q out + O back
         t_tc = flops / world / (peaks["bf16_tflops"] * 1e12)
         t_nv = sent / 770e9
         roof = max(t_tc, t_nv)
@@ -324,7 +334,7 @@ def run_ours(args):
                     "traffic": None, "peak_source": f"{peaks['source']} cuBLAS bf16 burst; NVLink 770 GB/s measured",
                     "exchanged_bytes_per_gpu": int(sent), "t_tensor_ms": t_tc * 1e3, "t_nvlink_ms": t_nv * 1e3}
     cpu_baseline = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not causal and VARIANT["D"] == 128:
         cv, sample = cpu_sample(H, S, budget_s=12.0)
         cpu_baseline = {"value": cv, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
 
@@ -454,6 +464,7 @@ def run_dit(args):
 
 if __name__ == "__main__":
     a = parse_args()
+    VARIANT["D"], VARIANT["causal"] = a.head_dim, a.causal
     if a.impl == "reference":
         run_reference(a)
     elif a.workload != "attention":

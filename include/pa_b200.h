@@ -73,6 +73,12 @@ typedef struct pa_attn_args {
     int64_t o_stride[3];
     int32_t* status;         /* device int or NULL */
     uint64_t wait_limit_ns;  /* 0 = default (2 s) */
+    /* Key-padding mask, or NULL when every key is valid: words written by pa_pack_key_mask with
+     * n_chunks = 1 and rows = seq_kv, [batch][ceil(seq_kv / 64)]. Masked keys take no part in the
+     * softmax: the same result as dropping them from k and v, which is what
+     * _attention_forward_sparse_kv does with index_select (src/para_attn/ops/__init__.py:248-299).
+     * A query row without any visible key comes out as zeros with an LSE of -inf. */
+    const uint64_t* key_bits;
 } pa_attn_args;
 
 int pa_attn_fwd(const pa_attn_args* args, void* stream);
@@ -142,9 +148,21 @@ typedef struct pa_cp_attn_args {
     int32_t pad_;
     int64_t q_pos[PA_MAX_CHUNKS];
     int64_t kv_pos[PA_MAX_CHUNKS];
+    /* Key-padding mask over all chunks, or NULL: [batch][n_kv_chunks][ceil(kv_rows / 64)] words
+     * from pa_pack_key_mask. Lifts the reference's "no mask with ring attention" limit
+     * (src/para_attn/para_attn_interface.py:228). */
+    const uint64_t* key_bits;
 } pa_cp_attn_args;
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);
+
+/* Packs a boolean key mask (one byte per key, non-zero = valid; [batch][n_chunks * rows] with the
+ * given batch stride in bytes) into the words the attention entry points read:
+ * out[batch][n_chunks][ceil(rows / 64)], bit i of a chunk's word i / 64 = key row i of that chunk.
+ * Replaces the index construction of _attention_forward_sparse_kv
+ * (src/para_attn/ops/__init__.py:271-283). */
+int pa_pack_key_mask(const uint8_t* mask, int64_t batch_stride, int32_t batch, int32_t n_chunks, int32_t rows,
+                     uint64_t* out, void* stream);
 
 /* Test hook: pa_attn_fwd that also dumps the raw q k^T tiles of the first CTA to dbg_s
  * ([2][kv_tiles][128][128] floats, may be NULL) and lets the caller choose the shared-memory

@@ -30,12 +30,16 @@ Array = np.ndarray
 # per-device attention (src/para_attn/ops/__init__.py:112-179)
 # --------------------------------------------------------------------------------------
 def sdpa_with_lse(q: Array, k: Array, v: Array, *, scale: Optional[float] = None, is_causal: bool = False,
-                  dtype=np.float32) -> Tuple[Array, Array]:
+                  dtype=np.float32, key_mask: Optional[Array] = None) -> Tuple[Array, Array]:
     """out = softmax(scale * q k^T [+ causal mask]) v and lse = logsumexp of the scaled logits.
 
     Mirrors what ``attention_forward_with_lse`` returns (src/para_attn/ops/__init__.py:160-179):
     ``out`` shaped like ``q``, ``lse`` of shape [B, H, S_q] holding the natural-log LSE. The
     causal mask is top-left aligned like torch SDPA. Shapes are [B, H, S, D].
+
+    ``key_mask`` ([B, S_kv] bool) drops keys the way ``_attention_forward_sparse_kv`` does
+    (src/para_attn/ops/__init__.py:271-292: per batch element, keep ``k[..., indices[m], :]``);
+    a batch element without any kept key yields zeros, as SDPA over zero keys does.
     """
     q = np.asarray(q, dtype=dtype)
     k = np.asarray(k, dtype=dtype)
@@ -47,11 +51,17 @@ def sdpa_with_lse(q: Array, k: Array, v: Array, *, scale: Optional[float] = None
         sq, sk = s.shape[-2], s.shape[-1]
         mask = np.tril(np.ones((sq, sk), dtype=bool))
         s = np.where(mask, s, dtype(-np.inf))
+    if key_mask is not None:
+        km = np.asarray(key_mask, dtype=bool)
+        s = np.where(km[:, None, None, :], s, dtype(-np.inf))
     m = s.max(axis=-1, keepdims=True)
+    dead = ~np.isfinite(m)            # rows without any visible key
+    m = np.where(dead, dtype(0), m)
     p = np.exp(s - m)
     l = p.sum(axis=-1, keepdims=True)
-    out = np.matmul(p / l, v)
-    lse = (m + np.log(l))[..., 0]
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = np.matmul(np.where(dead, dtype(0), p / np.where(dead, dtype(1), l)), v)
+        lse = np.where(dead, dtype(-np.inf), m + np.log(np.where(dead, dtype(1), l)))[..., 0]
     return out, lse
 
 

@@ -21,6 +21,8 @@ from .para_attn_interface import (  # noqa: E402
     InBatchAttnMode,
     ring_attn_func,
     RingAttnMode,
+    sparse_kv_attn_func,
+    SparseKVAttnMode,
     ulysses_attn_func,
     UlyssesAttnMode,
     UnifiedAttnMode,
@@ -32,6 +34,8 @@ __all__ = [
     "RingAttnMode",
     "UlyssesAttnMode",
     "InBatchAttnMode",
+    "SparseKVAttnMode",
+    "sparse_kv_attn_func",
     "ring_attn_func",
     "ulysses_attn_func",
     "in_batch_attn_func",
@@ -40,7 +44,7 @@ __all__ = [
 ]
 
 _SUBMODULES = (
-    "config", "ops", "primitives", "utils", "para_attn_interface",
+    "config", "ops", "primitives", "utils", "para_attn_interface", "sparse_attn",
     "context_parallel", "context_parallel.diffusers_adapters",
     "first_block_cache", "first_block_cache.utils", "first_block_cache.diffusers_adapters",
 )

@@ -241,17 +241,18 @@ def fused_push_ctas(plan: CpPlan, B: int, sq: int, ctas: int) -> int:
 
 def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
                      arrive_expect: int, wait_ns: int, stream: int, out_local: Optional[torch.Tensor],
-                     push: Optional["L.CpPushArgs"] = None, local_qkv=None, is_causal: bool = False) -> None:
+                     push: Optional["L.CpPushArgs"] = None, local_qkv=None, is_causal: bool = False,
+                     key_bits: Optional[torch.Tensor] = None) -> None:
     """Build the arguments (``build_attention_args``) and launch pa_cp_attn_fwd."""
     a = build_attention_args(plan, ws, par, shape, dtype, skv, scale, arrive_expect, wait_ns, out_local, push,
-                             local_qkv, is_causal)
+                             local_qkv, is_causal, key_bits)
     L.check(L.load().pa_cp_attn_fwd(C.byref(a), stream))
 
 
 def build_attention_args(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
                          arrive_expect: int, wait_ns: int, out_local: Optional[torch.Tensor],
                          push: Optional["L.CpPushArgs"] = None, local_qkv=None,
-                         is_causal: bool = False) -> "L.CpAttnArgs":
+                         is_causal: bool = False, key_bits: Optional[torch.Tensor] = None) -> "L.CpAttnArgs":
     """Arguments of pa_cp_attn_fwd for this rank. ``out_local`` (ring-only meshes) receives the result in
     place; otherwise tiles go to the owners' output staging buffers. With ``push`` the launch
     also performs this rank's part of the exchange (fused form). ``local_qkv`` = this rank's own
@@ -303,6 +304,9 @@ def build_attention_args(plan: CpPlan, ws: Workspace, par: int, shape, dtype: to
             a.q_pos[c] = plan.flat(c, plan.r) * sq
         for c in range(plan.world):
             a.kv_pos[c] = c * skv
+    if key_bits is not None:
+        assert key_bits.shape == (B, plan.world, (skv + 63) // 64) and key_bits.is_contiguous()
+        a.key_bits = key_bits.data_ptr()
     return a
 
 
@@ -378,9 +382,10 @@ class CpEngine:
             raise L.PaError(L.PA_ETIMEDOUT, L.DEV_STATUS_NAMES.get(st, f"device status {st}"))
 
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float],
-                  is_causal: bool = False) -> torch.Tensor:
+                  is_causal: bool = False, key_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """q: [B, H, s_q, D], k/v: [B, H, s_kv, D] local shards -> [B, H, s_q, D] local output.
-        ``is_causal`` masks over the whole sequence, shards taken in flat-rank order."""
+        ``is_causal`` masks over the whole sequence, shards taken in flat-rank order. ``key_mask``
+        ([B, world * s_kv] bool, the same on every rank) drops keys, chunks in flat-rank order."""
         B, H, sq, D = q.shape
         skv = k.shape[2]
         plan = CpPlan(self.ulysses, self.ring, self.u, self.r, H)
@@ -411,12 +416,18 @@ class CpEngine:
         out_local = None
         if self.ulysses == 1:
             out_local = torch.empty((B, sq, H, D), dtype=q.dtype, device=q.device).transpose(1, 2)
-        key = (B, H, sq, skv, D, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(), is_causal)
+        key_bits = None
+        if key_mask is not None:
+            from . import ops as _ops
+
+            key_bits = _ops.pack_key_mask(key_mask, self.world, skv)
+        key = (B, H, sq, skv, D, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(), is_causal,
+               key_bits is not None)
         ent = self._launch_cache.get(key)
         if ent is None:
             push = build_push_args(plan, ws, par, q, k, v, n_push)
             a = build_attention_args(plan, ws, par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par],
-                                     wait_ns, out_local, push, (q, k, v), is_causal)
+                                     wait_ns, out_local, push, (q, k, v), is_causal, key_bits)
             which = [js.tensor for js in plan.push_jobs(skip_self=True)]
             ent = (a, push, which)
             if len(self._launch_cache) > 64:
@@ -429,6 +440,8 @@ class CpEngine:
                 push.jobs[i].src = ptr[name]
             a.q_local, a.k_local, a.v_local = ptr["q"], ptr["k"], ptr["v"]
             a.flag_expect = st.arrive_expect[par]
+            if key_bits is not None:
+                a.key_bits = key_bits.data_ptr()
             if out_local is not None:
                 a.out[0] = out_local.data_ptr()
         L.check(L.load().pa_cp_attn_fwd(C.byref(a), main.cuda_stream))

@@ -38,6 +38,7 @@ class AttnArgs(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
         ("o_stride", C.c_int64 * 3),
         ("status", C.c_void_p), ("wait_limit_ns", C.c_uint64),
+        ("key_bits", C.c_void_p),
     ]
 
 
@@ -61,6 +62,7 @@ class CpAttnArgs(C.Structure):
         ("local_head_offset", C.c_int32), ("local_total_heads", C.c_int32),
         ("is_causal", C.c_int32), ("pad_", C.c_int32),
         ("q_pos", C.c_int64 * PA_MAX_CHUNKS), ("kv_pos", C.c_int64 * PA_MAX_CHUNKS),
+        ("key_bits", C.c_void_p),
     ]
 
 
@@ -108,6 +110,8 @@ def load() -> C.CDLL:
     lib.pa_dbg_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pa_cp_attn_fwd.restype = C.c_int
     lib.pa_cp_attn_fwd.argtypes = [C.POINTER(CpAttnArgs), C.c_void_p]
+    lib.pa_pack_key_mask.restype = C.c_int
+    lib.pa_pack_key_mask.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.pa_cp_push.restype = C.c_int
     lib.pa_cp_push.argtypes = [C.POINTER(CpPushArgs), C.c_void_p]
     lib.pa_flag_wait.restype = C.c_int

@@ -7,9 +7,10 @@ Attributes used: ``config.patch_size``, ``config.patch_size_t``, ``rope``, ``tim
 the sequence; each rank's joint sequence is [its video shard, its text shard].
 
 The reference builds a key-padding mask over video + text tokens, re-orders it to that
-interleaved layout and lets ``SparseKVAttnMode`` drop padded keys before attention. The
-chunked kernel has no key mask yet, so a prompt mask that is all-valid (the configuration the
-benchmarks use) is dropped - which is exact - and any padded prompt raises.
+interleaved layout (:74-100) and lets ``SparseKVAttnMode`` drop padded keys before attention
+(:112). Here the mask - in the same interleaved order, one [video shard, text shard] piece per
+rank of the sequence mesh - goes into the chunked attention kernel, which also works when the
+mesh has a ring dimension. A prompt mask without padding is dropped, which is exact.
 """
 import functools
 from typing import Any, Dict, Optional, Union
@@ -53,11 +54,18 @@ def parallelize_transformer(transformer, *, mesh=None):
         hidden_states = self.x_embedder(hidden_states)
         encoder_hidden_states = self.context_embedder(encoder_hidden_states, timestep, encoder_attention_mask)
 
-        if not bool(encoder_attention_mask.to(torch.bool).all()):
-            raise NotImplementedError(
-                "padded prompts (encoder_attention_mask with zeros) need a key mask in the attention kernel, "
-                "which is not built; pass prompts at full length")
         attention_mask = None  # every key is valid
+        prompt_mask = encoder_attention_mask.to(torch.bool)
+        if not bool(prompt_mask.all()):
+            world = DP.get_world_size(seq_mesh)
+            n_video, n_text = hidden_states.shape[1], encoder_hidden_states.shape[1]
+            assert n_video % world == 0 and n_text % world == 0, "sequence lengths must divide by the mesh size"
+            video = torch.ones(batch_size, n_video // world, dtype=torch.bool, device=prompt_mask.device)
+            pieces = []
+            for piece in prompt_mask.chunk(world, dim=-1):
+                pieces += [video, piece]
+            attention_mask = torch.cat(pieces, dim=-1)[:, None, None, :]
+            attention_mask = DP.get_assigned_chunk(attention_mask, dim=0, group=batch_mesh)
 
         temb = DP.get_assigned_chunk(temb, dim=0, group=batch_mesh)
         hidden_states = DP.get_assigned_chunk(hidden_states, dim=0, group=batch_mesh)

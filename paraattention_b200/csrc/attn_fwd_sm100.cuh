@@ -95,6 +95,10 @@ struct AttnParams {
     int causal;
     long long q_pos[PA_MAX_CHUNKS];
     long long kv_pos[PA_MAX_CHUNKS];
+    // key mask (NULL: every key is valid): bit i of word [batch][chunk][i / 64] tells whether key
+    // row i of that chunk may be attended to; strides in 64-bit words
+    const unsigned long long* key_bits;
+    long long kb_sb, kb_sc;
     // debug instantiation only
     float* dbg_s;      // raw S of CTA 0: [tile][kv tile][row][col]
     int v_lbo, v_sbo;  // B descriptor of V (bytes)
@@ -468,6 +472,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     const long long lim = q_here - (p.kv_pos[c_kv] + tk * kTileN + half * 64) + 1;
                     valid = static_cast<int>(lim < valid ? (lim < 0 ? 0 : lim) : valid);
                 }
+                // which of my 64 columns count: the key mask word (same for the whole warp), cut
+                // at the ragged end of the chunk and at the causal diagonal
+                unsigned long long live = ~0ull;
+                if (p.key_bits != nullptr && valid > 0)  // (a half tile past the chunk's end has no word)
+                    live = __ldg(p.key_bits + bidx * p.kb_sb + c_kv * p.kb_sc + tk * 2 + half);
+                if (valid < 64) live &= (valid <= 0) ? 0ull : ((1ull << valid) - 1ull);
                 dbg_stamp<kDebug>(p, t, j, 0, stamper);
                 // A wait that gives up does not leave the loop: the two partner warps must meet at
                 // every pair barrier below, and once the abort word is set no wait blocks any more.
@@ -493,12 +503,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                             for (int i = 0; i < 32; ++i) d[c * 32 + i] = __uint_as_float(s[c][i]);
                     }
-                    if (valid < 64) {
+                    if (live != ~0ull) {
 #pragma unroll
                         for (int c = 0; c < 2; ++c)
 #pragma unroll
                             for (int i = 0; i < 32; ++i)
-                                if (c * 32 + i >= valid) s[c][i] = 0xff800000u;  // -inf
+                                if (((live >> (c * 32 + i)) & 1ull) == 0) s[c][i] = 0xff800000u;  // -inf
                     }
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
@@ -516,7 +526,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const bool grow = (m_new - m_ref) * sl > kRescaleThreshold;
                 if (__any_sync(0xffffffffu, grow)) {  // same decision in both partner warps
                     // (a row that has seen no visible key yet keeps m = -inf: scale by 1, not by NaN)
-                    const float alpha = (kCausal && m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl);
+                    const float alpha = (m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl);
                     l_sum *= alpha;
                     m_ref = m_new;
                     if (j > 0) {
@@ -542,7 +552,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                         tc_fence_after();
                     }
                 }
-                const float neg = (kCausal && m_ref == -INFINITY) ? 0.0f : -m_ref * sl;
+                const float neg = (m_ref == -INFINITY) ? 0.0f : -m_ref * sl;
                 dbg_stamp<kDebug>(p, t, j, 3, stamper);
                 // p = 2^(s*sl - m*sl) in packed fp32x2 arithmetic. The exponentials are split between
                 // the special-function unit and an FMA-pipe polynomial so that neither pipe alone
@@ -560,10 +570,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     tmem_ld32(tS + c * 32, sc);
                     tc_wait_ld();
                     tmem_ld_fence(sc);
-                    if (valid < 64) {
+                    if (live != ~0ull) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i >= valid) sc[i] = 0xff800000u;  // -inf
+                            if (((live >> (c * 32 + i)) & 1ull) == 0) sc[i] = 0xff800000u;  // -inf
                     }
                     uint32_t pk[16];
 #pragma unroll
@@ -605,7 +615,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_fence_after();
             const int row = row0 + t * kTileM + row_in_tile;
             const bool in_range = row < p.q_rows;
-            const float inv = empty ? 0.0f : 1.0f / l_row;
+            // a row that saw no key (all masked) comes out as zeros with an LSE of -inf
+            const float inv = (empty || !(l_row > 0.0f)) ? 0.0f : 1.0f / l_row;
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
                              (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
                               static_cast<long long>(row) * p.o_ss) + half * (kD / 2);

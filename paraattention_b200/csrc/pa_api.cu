@@ -12,6 +12,7 @@
 #include "../../include/pa_b200.h"
 #include "attn_fwd_sm100.cuh"
 #include "fbc_sm100.cuh"
+#include "key_mask_sm100.cuh"
 #include "merge_sm100.cuh"
 
 namespace {
@@ -169,6 +170,9 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     p.l_sh = a->seq_q;
     p.status = a->status;
     p.wait_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
+    p.key_bits = reinterpret_cast<const unsigned long long*>(a->key_bits);
+    p.kb_sb = (a->seq_kv + 63) / 64;
+    p.kb_sc = 0;
     p.dbg_s = dbg_s;
     p.v_lbo = v_lbo;
     p.v_sbo = v_sbo;
@@ -328,6 +332,9 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     p.l_sb = a->lse_stride[0];
     p.l_sh = a->lse_stride[1];
     p.flag_expect = a->flag_expect;
+    p.key_bits = reinterpret_cast<const unsigned long long*>(a->key_bits);
+    p.kb_sc = (a->kv_rows + 63) / 64;
+    p.kb_sb = p.kb_sc * a->n_kv_chunks;
     p.status = a->status;
     p.wait_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
 
@@ -348,6 +355,21 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s, a->head_dim)
                                : launch_attn<false, false>(maps, p, push, int(grid), s, a->head_dim);
+}
+
+int pa_pack_key_mask(const uint8_t* mask, int64_t batch_stride, int32_t batch, int32_t n_chunks, int32_t rows,
+                     uint64_t* out, void* stream) {
+    if (mask == nullptr || out == nullptr) return fail(PA_EINVAL, "pack_key_mask: NULL pointer");
+    if (batch <= 0 || n_chunks <= 0 || rows <= 0) return fail(PA_EINVAL, "pack_key_mask: batch, n_chunks, rows must be positive");
+    if (batch_stride < int64_t(n_chunks) * rows) return fail(PA_EINVAL, "pack_key_mask: batch stride shorter than a row of keys");
+    const long long total = static_cast<long long>(batch) * n_chunks * ((rows + 63) / 64);
+    long long blocks = (total + 7) / 8;  // 8 warps per block
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    pa::pack_key_mask_kernel<<<int(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        mask, batch_stride, batch, n_chunks, rows, reinterpret_cast<unsigned long long*>(out));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "pack_key_mask launch: %s", cudaGetErrorString(e));
+    return PA_OK;
 }
 
 int pa_cp_push(const pa_cp_push_args* a, void* stream) {

@@ -20,6 +20,9 @@ from . import _lib as L
 __all__ = [
     "attention_forward_with_lse",
     "attention_forward",
+    "attention_forward_sparse_kv",
+    "key_mask_of",
+    "pack_key_mask",
     "merge_out_lse_",
     "raw_attention_forward",
 ]
@@ -33,7 +36,8 @@ def _check_inputs(query, key, value, attn_mask, dropout_p, is_causal):
     if query.dtype not in _DTYPES or key.dtype != query.dtype or value.dtype != query.dtype:
         raise NotImplementedError(f"attention dtype {query.dtype}: only bfloat16 and float16 are built")
     if attn_mask is not None:
-        raise NotImplementedError("attn_mask is not built into the sm_100a attention kernel")
+        raise NotImplementedError("attn_mask: only boolean key-padding masks are built into the sm_100a attention "
+                                  "kernel (torch.ops.para_attn.attention_forward_sparse_kv)")
     if dropout_p != 0.0:
         raise NotImplementedError("dropout_p must be 0: the library is forward/inference only")
     D = query.shape[-1]
@@ -52,8 +56,36 @@ def _tma_ready(x: torch.Tensor) -> torch.Tensor:
     return x if ok else x.contiguous()
 
 
+def key_mask_of(attn_mask: Optional[torch.Tensor], batch: int, keys: int) -> Optional[torch.Tensor]:
+    """The [batch, keys] boolean key-padding mask that ``attn_mask`` stands for, or None if it is
+    not one. The reference's sparse-KV path reads one row of key flags per batch element
+    (``while m.ndim > 1: m = m[0]``, src/para_attn/ops/__init__.py:279-280); here the mask must
+    say so itself: boolean, broadcastable to [batch, 1, 1, keys] with size-1 head and query dims."""
+    if attn_mask is None or attn_mask.dtype != torch.bool or attn_mask.ndim > 4 or attn_mask.ndim < 1:
+        return None
+    m = attn_mask
+    while m.ndim < 4:
+        m = m.unsqueeze(0)
+    if m.shape[1] != 1 or m.shape[2] != 1 or m.shape[3] != keys or m.shape[0] not in (1, batch):
+        return None
+    return m[:, 0, 0, :].expand(batch, keys)
+
+
+def pack_key_mask(key_mask: torch.Tensor, n_chunks: int, rows: int) -> torch.Tensor:
+    """pa_pack_key_mask: [batch, n_chunks * rows] bool -> [batch, n_chunks, ceil(rows / 64)] words
+    (int64 storage) as the attention entry points read them."""
+    assert key_mask.dtype == torch.bool and key_mask.ndim == 2 and key_mask.shape[1] == n_chunks * rows
+    assert key_mask.device.type == "cuda", "Must be CUDA tensors"
+    m = key_mask.contiguous()
+    out = torch.empty((m.shape[0], n_chunks, (rows + 63) // 64), dtype=torch.int64, device=m.device)
+    L.check(L.load().pa_pack_key_mask(m.data_ptr(), m.stride(0), m.shape[0], n_chunks, rows, out.data_ptr(),
+                                      torch.cuda.current_stream(m.device).cuda_stream))
+    return out
+
+
 def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: bool,
-                          status: Optional[torch.Tensor] = None, is_causal: bool = False):
+                          status: Optional[torch.Tensor] = None, is_causal: bool = False,
+                          key_mask: Optional[torch.Tensor] = None):
     """Launch pa_attn_fwd on the current stream. Output memory is [B, S, H, D] viewed as
     [B, H, S, D], the layout PyTorch's flash backend returns, so that the usual
     ``transpose(1, 2).flatten(2)`` that follows attention is free."""
@@ -73,6 +105,8 @@ def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: b
         a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
     a.status = status.data_ptr() if status is not None else None
     a.wait_limit_ns = 0
+    bits = pack_key_mask(key_mask, 1, Skv) if key_mask is not None else None
+    a.key_bits = bits.data_ptr() if bits is not None else None
     L.check(L.load().pa_attn_fwd(C.byref(a), torch.cuda.current_stream(query.device).cuda_stream))
     return out, lse
 
@@ -118,6 +152,41 @@ def attention_forward(
 
 
 @torch.library.register_fake("para_attn::attention_forward")
+def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None):
+    B, H, Sq, D = query.shape
+    return query.new_empty((B, Sq, H, D)).transpose(1, 2)
+
+
+@torch.library.custom_op("para_attn::attention_forward_sparse_kv", mutates_args=(), device_types=("cuda",))
+def attention_forward_sparse_kv(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attn_mask: Optional[torch.Tensor] = None,
+    dropout_p: float = 0.0,
+    is_causal: bool = False,
+    *,
+    scale: Optional[float] = None,
+) -> torch.Tensor:
+    """Attention over the keys a boolean key-padding mask keeps
+    (src/para_attn/ops/__init__.py:248-343). The reference gathers the kept keys per batch element
+    and runs SDPA on each; here the kernel masks the dropped keys in place, one launch for the
+    whole batch. A query whose keys are all dropped yields zeros."""
+    if attn_mask is None:
+        _check_inputs(query, key, value, None, dropout_p, is_causal)
+        return raw_attention_forward(query, key, value, scale, False, is_causal=is_causal)[0]
+    assert attn_mask.dtype == torch.bool, "attn_mask must be a boolean tensor"
+    assert not is_causal, "is_causal is not supported with sparse kv"
+    _check_inputs(query, key, value, None, dropout_p, is_causal)
+    km = key_mask_of(attn_mask, query.shape[0], key.shape[2])
+    if km is None:
+        raise NotImplementedError(
+            f"attn_mask of shape {tuple(attn_mask.shape)}: expected a key-padding mask broadcastable to "
+            f"[{query.shape[0]}, 1, 1, {key.shape[2]}]")
+    return raw_attention_forward(query, key, value, scale, False, key_mask=km)[0]
+
+
+@torch.library.register_fake("para_attn::attention_forward_sparse_kv")
 def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None):
     B, H, Sq, D = query.shape
     return query.new_empty((B, Sq, H, D)).transpose(1, 2)

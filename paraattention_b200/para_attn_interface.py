@@ -30,10 +30,20 @@ __all__ = [
     "ulysses_attn_func",
     "in_batch_attn_func",
     "unified_attn_func",
+    "sparse_kv_attn_func",
+    "SparseKVAttnMode",
 ]
 
 
-def _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal) -> bool:
+def _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal, total_keys=None) -> bool:
+    """Whether the sm_100a kernel covers this call. A mask is covered when it is a boolean
+    key-padding mask over ``total_keys`` keys (default: the keys of ``key``) and the call is not causal."""
+    if attn_mask is not None:
+        if query.ndim != 4 or is_causal:
+            return False
+        n = key.shape[-2] if total_keys is None else total_keys
+        if para_attn_ops.key_mask_of(attn_mask, query.shape[0], n) is None:
+            return False
     return (
         query.device.type == "cuda"
         and query.dtype in (torch.bfloat16, torch.float16)
@@ -43,7 +53,6 @@ def _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal) -> bool:
         and query.shape[-1] in (64, 128)
         and key.shape[-1] == query.shape[-1]
         and value.shape[-1] == query.shape[-1]
-        and attn_mask is None
         and dropout_p == 0.0
     )
 
@@ -52,6 +61,8 @@ def _local_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal
     """The non-parallel SDPA at the bottom of every mode (state "none" of the reference,
     src/para_attn/para_attn_interface.py:468-475)."""
     if _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal):
+        if attn_mask is not None:
+            return para_attn_ops.attention_forward_sparse_kv(query, key, value, attn_mask=attn_mask, scale=scale)
         return para_attn_ops.attention_forward(query, key, value, is_causal=is_causal, scale=scale)
     if get_force_dispatch_to_custom_ops():
         return para_attn_ops.attention_forward(
@@ -60,17 +71,24 @@ def _local_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal
         query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale)
 
 
-def _cp_attention(query, key, value, scale, *, flat_group, ulysses, ring, u, r, is_causal=False):
+def _cp_attention(query, key, value, scale, *, flat_group, ulysses, ring, u, r, is_causal=False, attn_mask=None):
     assert query.device.type == "cuda", "Must be CUDA tensors"
     eng = _cp_engine.get_engine(flat_group, ulysses, ring, u, r, query.device)
-    return eng.attention(query, key, value, scale, is_causal=bool(is_causal))
+    key_mask = None
+    if attn_mask is not None:
+        # keys of all ranks, chunk by chunk in flat-rank order: for a Ulysses group that is the
+        # order its all-to-all produces (src/para_attn/para_attn_interface.py:60-72), the layout
+        # the reference's adapters build their masks in
+        key_mask = para_attn_ops.key_mask_of(attn_mask, query.shape[0], ulysses * ring * key.shape[2])
+    return eng.attention(query, key, value, scale, is_causal=bool(is_causal), key_mask=key_mask)
 
 
-def _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, what):
-    if not _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal):
+def _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, what, world=1):
+    if not _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal, total_keys=world * key.shape[-2]):
         raise NotImplementedError(
             f"{what}: the context-parallel kernel is built for CUDA bf16/f16 tensors with head_dim 64 or 128, "
-            "no mask, no dropout")
+            "no dropout, and no mask other than a boolean key-padding mask [B, 1, 1, keys of all ranks] "
+            "(not together with is_causal)")
 
 
 def ulysses_attn_func(
@@ -102,9 +120,9 @@ def ulysses_attn_func(
         raise NotImplementedError(
             "ulysses_attn_func with a custom attn_func: the head<->sequence exchange is fused into the attention "
             "kernel and cannot wrap a foreign attention function")
-    _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "ulysses_attn_func")
+    _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "ulysses_attn_func", world_size)
     return _cp_attention(query, key, value, scale, flat_group=pg, ulysses=world_size, ring=1,
-                         u=DP.get_rank(pg), r=0, is_causal=is_causal)
+                         u=DP.get_rank(pg), r=0, is_causal=is_causal, attn_mask=attn_mask)
 
 
 def ring_attn_func(
@@ -124,10 +142,14 @@ def ring_attn_func(
         return _local_attention(query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal,
                                 scale=scale)
 
-    assert attn_mask is None, "attn_mask is not supported in ring_attn_func when world_size > 1"
-    _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "ring_attn_func")
+    # The reference asserts attn_mask is None here (src/para_attn/para_attn_interface.py:228); a
+    # boolean key-padding mask over the keys of all ranks is the one kind that is accepted.
+    assert attn_mask is None or (query.ndim == 4 and para_attn_ops.key_mask_of(
+        attn_mask, query.shape[0], world_size * key.shape[-2]) is not None), \
+        "attn_mask is not supported in ring_attn_func when world_size > 1"
+    _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "ring_attn_func", world_size)
     return _cp_attention(query, key, value, scale, flat_group=pg, ulysses=1, ring=world_size, u=0,
-                         r=DP.get_rank(pg), is_causal=is_causal)
+                         r=DP.get_rank(pg), is_causal=is_causal, attn_mask=attn_mask)
 
 
 def unified_attn_func(
@@ -156,11 +178,14 @@ def unified_attn_func(
         return ring_attn_func(query, key, value, attn_mask, dropout_p, is_causal, scale=scale, mesh=ring_mesh)
     assert query.ndim == 4, "query must have 4 dimensions, got {}".format(query.ndim)
     assert query.shape[1] % U == 0, "h must be divisible by world_size, got {} and {}".format(query.shape[1], U)
-    assert attn_mask is None, "attn_mask is not supported in ring_attn_func when world_size > 1"
+    assert attn_mask is None or para_attn_ops.key_mask_of(
+        attn_mask, query.shape[0], U * R * key.shape[-2]) is not None, \
+        "attn_mask is not supported in ring_attn_func when world_size > 1"
     assert flat_group is not None, "a process group spanning the ulysses x ring ranks is required"
-    _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "unified attention")
+    _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, "unified attention", U * R)
     return _cp_attention(query, key, value, scale, flat_group=flat_group, ulysses=U, ring=R,
-                         u=DP.get_rank(ulysses_mesh), r=DP.get_rank(ring_mesh), is_causal=is_causal)
+                         u=DP.get_rank(ulysses_mesh), r=DP.get_rank(ring_mesh), is_causal=is_causal,
+                         attn_mask=attn_mask)
 
 
 def in_batch_attn_func(
@@ -333,6 +358,50 @@ class UnifiedAttnMode(_AttnModeBase):
                                  flat_group=self._flat_group)
 
     _call_unified_attn_func = _call_attn_func
+
+
+def sparse_kv_attn_func(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None,
+                        dispatch_to_custom_ops=True):
+    """Attention that drops the keys a boolean key-padding mask marks False
+    (src/para_attn/sparse_attn.py:14-69). Both dispatch settings run the same kernel."""
+    return para_attn_ops.attention_forward_sparse_kv(query, key, value, attn_mask=attn_mask, dropout_p=dropout_p,
+                                                     is_causal=is_causal, scale=scale)
+
+
+class SparseKVAttnMode(BaseTorchFunctionMode):
+    """Routes ``F.scaled_dot_product_attention`` to ``sparse_kv_attn_func``
+    (src/para_attn/sparse_attn.py:607-640)."""
+
+    disabled = False
+
+    @torch.compiler.disable
+    def __init__(self, *, dispatch_to_custom_ops=True):
+        super().__init__()
+        self._dispatch_to_custom_ops = dispatch_to_custom_ops
+
+    def __torch_function__(self, func, types, args=(), kwargs=None):
+        kwargs = {} if kwargs is None else kwargs
+        if SparseKVAttnMode.disabled:
+            return base_handle_torch_function(func, types, args, kwargs)
+        if func is F.scaled_dot_product_attention:
+            return sparse_kv_attn_func(*args, **kwargs, dispatch_to_custom_ops=self._dispatch_to_custom_ops)
+        return base_handle_torch_function(func, types, args, kwargs)
+
+    @classmethod
+    @contextlib.contextmanager
+    def disable(cls):
+        old_disabled = cls._set_disabled(True)
+        try:
+            yield
+        finally:
+            cls._set_disabled(old_disabled)
+
+    @classmethod
+    @torch.compiler.disable
+    def _set_disabled(cls, value):
+        old_disabled = cls.disabled
+        cls.disabled = value
+        return old_disabled
 
 
 class InBatchAttnMode(_AttnModeBase):

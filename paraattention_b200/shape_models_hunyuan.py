@@ -136,11 +136,16 @@ class HunyuanVideoShapedTransformer3DModel(nn.Module, _DeviceMixin):
         temb = self.time_text_embed(timestep, guidance, pooled_projections)
         hidden_states = self.x_embedder(hidden_states)
         encoder_hidden_states = self.context_embedder(encoder_hidden_states, timestep, encoder_attention_mask)
+        # key-padding mask over [video tokens, prompt tokens]; None when the prompt has no padding
+        attention_mask = None
+        if encoder_attention_mask is not None and not bool(encoder_attention_mask.to(torch.bool).all()):
+            video = torch.ones(batch_size, hidden_states.shape[1], dtype=torch.bool, device=hidden_states.device)
+            attention_mask = torch.cat([video, encoder_attention_mask.to(torch.bool)], dim=1)[:, None, None, :]
         for block in self.transformer_blocks:
-            hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, None,
+            hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, attention_mask,
                                                          image_rotary_emb)
         for block in self.single_transformer_blocks:
-            hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, None,
+            hidden_states, encoder_hidden_states = block(hidden_states, encoder_hidden_states, temb, attention_mask,
                                                          image_rotary_emb)
         hidden_states = self.proj_out(self.norm_out(hidden_states, temb))
         hidden_states = hidden_states.reshape(batch_size, ppf, pph, ppw, -1, p_t, p, p)

@@ -9,6 +9,7 @@ Writes
   cp_attention_w2.npz   world 2: ulysses_attn_func, ring_attn_func (non-causal and causal)
   cp_attention_w4.npz   world 4: UnifiedAttnMode on a 2x2 (ring x ulysses) mesh, RingAttnMode on 4
   fbcache_steps.npz     CachedTransformerBlocks decisions over a scripted bf16 sequence
+  sparse_kv.npz         _attention_forward_sparse_kv (key-padding masks, batch 3) on one process
 
 The only change made to the reference is the rebinding of
 ``para_attn.ops._attention_forward_with_lse`` (which asserts CUDA tensors at
@@ -197,12 +198,33 @@ def make_fbcache(ref: str):
     np.savez_compressed(HERE / "fbcache_steps.npz", **store)
 
 
+def make_sparse_kv(ref: str):
+    """The reference's key-dropping attention (src/para_attn/ops/__init__.py:248-299) run as is on
+    CPU in fp32: batch 3 with a prefix mask, a scattered mask and an all-valid row of flags."""
+    sys.path.insert(0, ref)
+    import para_attn.ops as ref_ops
+
+    Bm, Hm, Sq, Skv = 3, 1, 48, 160
+    g = torch.Generator().manual_seed(99)
+    q = torch.randn(Bm, Hm, Sq, D, generator=g).bfloat16()
+    k = torch.randn(Bm, Hm, Skv, D, generator=g).bfloat16()
+    v = torch.randn(Bm, Hm, Skv, D, generator=g).bfloat16()
+    mask = torch.ones(Bm, 1, 1, Skv, dtype=torch.bool)
+    mask[0, ..., 97:] = False                                     # padded tail
+    mask[1] = torch.rand(1, 1, Skv, generator=g) < 0.6             # scattered
+    out = ref_ops._attention_forward_sparse_kv(q.float(), k.float(), v.float(), attn_mask=mask)
+    np.savez_compressed(HERE / "sparse_kv.npz", q=bits(q), k=bits(k), v=bits(v), mask=mask.numpy(), out=out.numpy())
+    print("sparse_kv", tuple(out.shape), "kept keys per batch element:", mask.sum(dim=-1).flatten().tolist())
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default="/root/reference/src")
-    ap.add_argument("--only", choices=["attention", "fbcache"], default=None)
+    ap.add_argument("--only", choices=["attention", "fbcache", "sparse_kv"], default=None)
     args = ap.parse_args()
     if args.only in (None, "attention"):
         make_attention(args.ref)
     if args.only in (None, "fbcache"):
         make_fbcache(args.ref)
+    if args.only in (None, "sparse_kv"):
+        make_sparse_kv(args.ref)

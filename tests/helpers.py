@@ -105,7 +105,8 @@ class LocalCluster:
         assert code == 0, f"device status {code}"
         return out
 
-    def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000, in_place=True, is_causal=False):
+    def attention(self, qs, ks, vs, scale=None, ctas=4, wait_ns=200_000_000, in_place=True, is_causal=False,
+                  key_mask=None):
         E = self.E
         B, H, sq, D = qs[0].shape
         skv = ks[0].shape[2]
@@ -126,12 +127,17 @@ class LocalCluster:
             import ctypes as C
 
             L.check(L.load().pa_cp_push(C.byref(pa), stream))
+        key_bits = None
+        if key_mask is not None:  # [B, W * skv] bool, the same on every rank
+            from paraattention_b200 import ops
+
+            key_bits = ops.pack_key_mask(key_mask, self.W, skv)
         outs = [None] * self.W
         for g in range(self.W):
             if self.U == 1:
                 outs[g] = torch.empty((B, sq, H, D), dtype=qs[g].dtype, device=self.device).transpose(1, 2)
             E.launch_attention(plans[g], self.ws[g], par, (B, H, sq, D), qs[g].dtype, skv, scale, st.arrive_expect[par],
-                               wait_ns, stream, outs[g], None, keep[g] if in_place else None, is_causal)
+                               wait_ns, stream, outs[g], None, keep[g] if in_place else None, is_causal, key_bits)
         if self.U > 1:
             st.done_expect[par] += E.out_tiles_per_call(plans[0], B, sq)
             for g in range(self.W):

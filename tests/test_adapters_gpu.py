@@ -147,11 +147,13 @@ def _cp_worker(rank, world, port, ring, ret):
     want = hun(x, t, enc, mask, pooled, guidance=g).sample
     got = parallelize_transformer(hun, mesh=mesh)(x, t, enc, mask, pooled, guidance=g).sample
     errs["hunyuan"] = ((got.float() - want.float()).norm() / want.float().norm()).item()
-    try:
-        hun(x, t, enc, torch.tensor([[1, 1, 1, 1, 1, 1, 0, 0]], device="cuda"), pooled, guidance=g)
-        errs["padded_prompt_refused"] = False
-    except NotImplementedError:
-        errs["padded_prompt_refused"] = True
+    # a padded prompt: the key mask travels into the chunked kernel (also with a ring dimension)
+    padded = torch.tensor([[1, 1, 1, 1, 1, 0, 0, 0]], device="cuda")
+    want = _tiny_hunyuan()(x, t, enc, padded, pooled, guidance=g).sample
+    got = hun(x, t, enc, padded, pooled, guidance=g).sample
+    errs["hunyuan_padded_prompt"] = ((got.float() - want.float()).norm() / want.float().norm()).item()
+    errs["padding_matters"] = ((want.float() - hun(x, t, enc, mask, pooled, guidance=g).sample.float()).norm()
+                               / want.float().norm()).item() > 1e-3
     torch.cuda.synchronize()
     pa.check_device_status()
     if rank == 0:
@@ -174,6 +176,6 @@ def test_context_parallel_adapters_two_gpus(ring):
     errs = ret.get(timeout=300)
     for p in procs:
         p.join(timeout=60)
-    assert errs.pop("padded_prompt_refused")
+    assert errs.pop("padding_matters"), "the padded prompt gave the same result as the full one"
     for name, e in errs.items():
         assert e < 3e-2, f"{name}: relative L2 error {e:.3e} against the unsharded model"

@@ -13,7 +13,7 @@ from helpers import (assert_attention_close, assert_lse_close, bf16_from_bits, o
 pytestmark = pytest.mark.gpu
 
 
-def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is_causal=False):
+def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is_causal=False, key_bits=None):
     from paraattention_b200 import _lib as L
 
     lib = L.load()
@@ -28,6 +28,7 @@ def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is
     a.dtype = L.PA_BF16 if q.dtype == torch.bfloat16 else L.PA_F16
     a.scale = 1.0 / math.sqrt(D) if scale is None else scale
     a.is_causal = int(is_causal)
+    a.key_bits = key_bits.data_ptr() if key_bits is not None else None
     for i in range(3):
         a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
     a.status = status.data_ptr() if status is not None else None
@@ -158,6 +159,77 @@ def test_abi_rejects_bad_arguments():
     buf = torch.zeros(128 * 128 + 8, dtype=torch.bfloat16, device="cuda")
     rc, _, _ = _abi_attention(buf[3:3 + 127 * 128].view(1, 1, 127, 128), k, v)
     assert rc == L.PA_EINVAL  # base pointer not 16-byte aligned
+
+
+def _abi_pack(mask2d, n_chunks, rows):
+    from paraattention_b200 import _lib as L
+
+    out = torch.full((mask2d.shape[0], n_chunks, (rows + 63) // 64), -1, dtype=torch.int64, device="cuda")
+    rc = L.load().pa_pack_key_mask(mask2d.data_ptr(), mask2d.stride(0), mask2d.shape[0], n_chunks, rows,
+                                   out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    return out
+
+
+@pytest.mark.parametrize("B,n_chunks,rows", [(1, 1, 1), (2, 1, 64), (3, 2, 65), (2, 8, 4095), (1, 4, 130)])
+def test_pack_key_mask_is_bit_exact(B, n_chunks, rows):
+    g = torch.Generator().manual_seed(rows)
+    mask = (torch.rand(B, n_chunks * rows, generator=g) < 0.7).cuda()
+    words = _abi_pack(mask, n_chunks, rows).cpu().numpy().view(np.uint64)
+    m = mask.cpu().numpy().reshape(B, n_chunks, rows)
+    pad = (-rows) % 64
+    m = np.pad(m, ((0, 0), (0, 0), (0, pad)))
+    want = np.packbits(m.reshape(B, n_chunks, -1, 64), axis=-1, bitorder="little").view(np.uint64)[..., 0]
+    assert np.array_equal(words, want)
+
+
+def test_key_mask_against_reference_sparse_kv(golden_dir):
+    """Key-padding masks: the ABI, the custom op and SparseKVAttnMode against the output of the
+    reference's own _attention_forward_sparse_kv (fixture) and the oracle."""
+    import torch.nn.functional as F
+
+    import paraattention_b200 as pa
+
+    g = np.load(golden_dir / "sparse_kv.npz")
+    q, k, v = (bf16_from_bits(g[n]) for n in ("q", "k", "v"))
+    mask = torch.from_numpy(g["mask"]).cuda()
+    bits = _abi_pack(mask[:, 0, 0, :].contiguous(), 1, k.shape[2])
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc, out, lse = _abi_attention(q, k, v, status=status, key_bits=bits)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    assert_attention_close(out, g["out"], "sparse kv through the ABI")
+    _, ref_lse = O.sdpa_with_lse(*(t.float().cpu().numpy() for t in (q, k, v)), key_mask=g["mask"][:, 0, 0, :])
+    assert_lse_close(lse, ref_lse)
+    assert_attention_close(torch.ops.para_attn.attention_forward_sparse_kv(q, k, v, mask), g["out"], "custom op")
+    with pa.SparseKVAttnMode():
+        assert_attention_close(F.scaled_dot_product_attention(q, k, v, attn_mask=mask), g["out"], "SparseKVAttnMode")
+    assert_attention_close(pa.sparse_kv_attn_func(q, k, v), oracle_attention(q, k, v)[0], "no mask")
+    with pytest.raises(AssertionError):
+        pa.sparse_kv_attn_func(q, k, v, mask.float())
+    with pytest.raises(NotImplementedError):
+        pa.sparse_kv_attn_func(q, k, v, mask.expand(-1, -1, q.shape[2], -1))
+    # a batch element whose keys are all dropped comes out as zeros, LSE -inf
+    none = mask.clone()
+    none[1] = False
+    bits = _abi_pack(none[:, 0, 0, :].contiguous(), 1, k.shape[2])
+    rc, out, lse = _abi_attention(q, k, v, key_bits=bits)
+    assert rc == 0
+    assert (out[1] == 0).all() and torch.isneginf(lse[1]).all() and torch.isfinite(out.float()).all()
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv,D", [(2, 3, 515, 1000, 128), (1, 2, 300, 4095, 128), (2, 2, 257, 130, 64)])
+def test_key_mask_shapes_match_oracle(B, H, Sq, Skv, D):
+    q, k, v = seeded_qkv(B, H, Sq, Skv, D=D, seed=Sq + Skv)
+    g = torch.Generator().manual_seed(Skv)
+    mask = torch.rand(B, Skv, generator=g) < 0.5
+    mask[0, Skv // 3:] = False  # a long masked tail: whole tiles without a visible key
+    from paraattention_b200 import ops
+
+    out = ops.attention_forward_sparse_kv(q, k, v, mask[:, None, None, :].cuda())
+    ref, _ = O.sdpa_with_lse(*(t.float().cpu().numpy() for t in (q, k, v)), key_mask=mask.numpy())
+    assert_attention_close(out, ref, f"key mask B{B} H{H} Sq{Sq} Skv{Skv} D{D}")
 
 
 def test_golden_single_device(golden_dir):

@@ -78,6 +78,24 @@ def test_head_dim_64_meshes_against_oracle(U, R, H, S, causal):
         assert_attention_close(outs[rank], ref[rank], f"D64 causal={causal} {U}x{R} rank {rank}")
 
 
+@pytest.mark.parametrize("U,R,H,S,D", [(2, 1, 4, 2 * 515, 128), (1, 2, 2, 2 * 300, 128), (2, 2, 4, 4 * 257, 128),
+                                       (4, 2, 8, 8 * 131, 64), (1, 8, 2, 8 * 129, 128)])
+def test_key_mask_meshes_against_oracle(U, R, H, S, D):
+    """A key-padding mask over the keys of all ranks (chunks in flat-rank order), on Ulysses, ring
+    and mixed meshes: equal to masked attention over the whole sequence."""
+    W = U * R
+    B = 2
+    q, k, v = seeded_qkv(B, H, S, S, D=D, seed=U * 10 + R + 300)
+    g = torch.Generator().manual_seed(S)
+    mask = torch.rand(B, S, generator=g) < 0.6
+    mask[1, S - S // W - 7:] = False  # the last rank's keys are all padding for batch element 1
+    qs, ks, vs = ([t.contiguous() for t in x.chunk(W, dim=-2)] for x in (q, k, v))
+    outs = LocalCluster(U, R).attention(qs, ks, vs, key_mask=mask.cuda())
+    whole, _ = O.sdpa_with_lse(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(),
+                               key_mask=mask.numpy())
+    assert_attention_close(torch.cat(outs, dim=-2), whole, f"key mask {U}x{R}")
+
+
 @pytest.mark.parametrize("name,U,R", [("ulysses_short_kv", 2, 1), ("ring_short_kv", 1, 2)])
 def test_world2_short_kv_against_reference_outputs(golden_dir, name, U, R):
     g = np.load(golden_dir / "cp_attention_w2.npz")
@@ -192,6 +210,10 @@ def _mp_worker(rank, world, port, mode, ret):
             out = pa.ring_attn_func(qs, ks, vs, is_causal=True)
         elif mode == "ulysses_causal":
             out = pa.ulysses_attn_func(qs, ks, vs, is_causal=True)
+        elif mode in ("ulysses_mask", "ring_mask"):
+            mask = (torch.rand(1, 1, 1, S, generator=torch.Generator().manual_seed(5)) < 0.6).cuda()
+            fn = pa.ulysses_attn_func if mode == "ulysses_mask" else pa.ring_attn_func
+            out = fn(qs, ks, vs, attn_mask=mask)
         elif mode == "ring_d64_causal":
             with pa.RingAttnMode():
                 out = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True)
@@ -215,7 +237,7 @@ def _mp_worker(rank, world, port, mode, ret):
 
 
 @pytest.mark.parametrize("mode", ["ulysses", "ring", "unified", "ring_causal", "ulysses_causal", "ring_d64_causal",
-                                  "ulysses_d64"])
+                                  "ulysses_d64", "ulysses_mask", "ring_mask"])
 def test_multi_gpu_processes(mode):
     n = torch.cuda.device_count()
     if n < 2:
@@ -228,7 +250,7 @@ def test_multi_gpu_processes(mode):
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
     port = 29700 + {"ulysses": 1, "ring": 2, "unified": 3, "ring_causal": 4, "ulysses_causal": 5, "ring_d64_causal": 6,
-                    "ulysses_d64": 7}[mode]
+                    "ulysses_d64": 7, "ulysses_mask": 8, "ring_mask": 9}[mode]
     procs = [ctx.Process(target=_mp_worker, args=(r, world, port, mode, ret)) for r in range(world)]
     for p in procs:
         p.start()
@@ -238,6 +260,9 @@ def test_multi_gpu_processes(mode):
     assert same, "repeated calls gave different results"
     H, S = 4, world * 515
     q, k, v = seeded_qkv(1, H, S, S, D=64 if "d64" in mode else 128, seed=21, device="cpu")
+    key_mask = None
+    if mode.endswith("mask"):
+        key_mask = (torch.rand(1, 1, 1, S, generator=torch.Generator().manual_seed(5)) < 0.6)[:, 0, 0, :].numpy()
     ref, _ = O.sdpa_with_lse(q.float().numpy(), k.float().numpy(), v.float().numpy(),
-                             is_causal=mode.endswith("causal"))
+                             is_causal=mode.endswith("causal"), key_mask=key_mask)
     assert_attention_close(torch.from_numpy(full), ref, f"{mode} world {world}")

@@ -106,3 +106,23 @@ def test_fbcache_decisions(golden_dir, case, kw):
         first_residual = O.bf16_round(h1[t] - h0[t])  # bf16 tensor subtraction, utils.py:359
         hits.append(state.step(first_residual))
     assert hits == list(g[f"{case}_hit"])
+
+
+def test_key_mask_against_reference_sparse_kv(golden_dir):
+    """sdpa_with_lse(key_mask=...) against the reference's own _attention_forward_sparse_kv."""
+    g = np.load(golden_dir / "sparse_kv.npz")
+    q, k, v = (_f32(g[n]) for n in ("q", "k", "v"))
+    mask = g["mask"][:, 0, 0, :]
+    out, lse = O.sdpa_with_lse(q, k, v, key_mask=mask)
+    np.testing.assert_allclose(out, g["out"], rtol=1e-5, atol=2e-6)
+    assert np.isfinite(lse).all()
+    # dropping keys == gathering the kept keys, batch element by batch element
+    for b in range(q.shape[0]):
+        keep = np.nonzero(mask[b])[0]
+        o_b, l_b = O.sdpa_with_lse(q[b:b + 1], k[b:b + 1, :, keep], v[b:b + 1, :, keep])
+        np.testing.assert_allclose(out[b:b + 1], o_b, rtol=1e-5, atol=2e-6)
+        np.testing.assert_allclose(lse[b:b + 1], l_b, rtol=1e-5, atol=2e-6)
+    # a batch element without any kept key: zeros and an LSE of -inf
+    none = np.zeros_like(mask)
+    out0, lse0 = O.sdpa_with_lse(q, k, v, key_mask=none)
+    assert (out0 == 0).all() and np.isneginf(lse0).all()
