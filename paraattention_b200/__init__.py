@@ -28,6 +28,7 @@ from .para_attn_interface import (  # noqa: E402
     UnifiedAttnMode,
 )
 from ._cp_engine import check_device_status  # noqa: E402
+from .host_io import attention_from_host  # noqa: E402
 
 __all__ = [
     "UnifiedAttnMode",
@@ -40,6 +41,7 @@ __all__ = [
     "ulysses_attn_func",
     "in_batch_attn_func",
     "check_device_status",
+    "attention_from_host",
     "install_as_para_attn",
 ]
 

@@ -232,6 +232,28 @@ def test_key_mask_shapes_match_oracle(B, H, Sq, Skv, D):
     assert_attention_close(out, ref, f"key mask B{B} H{H} Sq{Sq} Skv{Skv} D{D}")
 
 
+@pytest.mark.parametrize("B,H,Sq,Skv,groups,causal", [(1, 4, 515, 1000, 2, False), (2, 6, 300, 300, 3, True),
+                                                      (1, 2, 129, 64, None, False)])
+def test_attention_from_host_matches_oracle(B, H, Sq, Skv, groups, causal):
+    """Host tensors in, host tensor out, pipelined over groups of heads on three streams."""
+    import paraattention_b200 as pa
+
+    q, k, v = seeded_qkv(B, H, Sq, Skv, seed=Sq + H, device="cpu")
+    q, k, v = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    out = pa.attention_from_host(q, k, v, is_causal=causal, head_groups=groups)
+    torch.cuda.synchronize()
+    assert out.device.type == "cpu" and out.shape == q.shape and out.is_pinned()
+    ref, _ = O.sdpa_with_lse(q.float().numpy(), k.float().numpy(), v.float().numpy(), is_causal=causal)
+    assert_attention_close(out, ref, "attention_from_host")
+    # a second call into a caller's buffer reuses the staging and gives the same bits
+    mine = torch.empty_like(q).pin_memory()
+    assert pa.attention_from_host(q, k, v, mine, is_causal=causal, head_groups=groups) is mine
+    torch.cuda.synchronize()
+    assert torch.equal(mine, out)
+    with pytest.raises(AssertionError):
+        pa.attention_from_host(q.cuda(), k, v)
+
+
 def test_golden_single_device(golden_dir):
     g = np.load(golden_dir / "cp_attention_w2.npz")
     q, k, v = (bf16_from_bits(g[n]) for n in ("q", "k", "v"))
