@@ -207,7 +207,9 @@ typedef struct pa_cp_push_args {
     int32_t n_dest;
     uint32_t* flag[PA_MAX_CHUNKS];
     int32_t ctas_per_dest;
-    int32_t first_dest;      /* destinations are served in the order first_dest, first_dest + 1, ... */
+    int32_t first_dest;      /* fused form: destinations are served in the order first_dest,
+                              * first_dest - 1, ... (mod n_dest), the order in which consumers
+                              * that walk their chunks upwards from their own rank need them */
 } pa_cp_push_args;
 
 int pa_cp_push(const pa_cp_push_args* args, void* stream);

@@ -229,7 +229,7 @@ def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int,
         # counter slot on the destination = my plan rank (= chunk slot of my K/V there)
         pa.flag[d] = ws.peer[d] + lay.off_arrive[par] + 4 * plan.rank
     pa.ctas_per_dest = ctas
-    pa.first_dest = plan.rank  # own buffer first, then the peers in ring order
+    pa.first_dest = plan.rank  # own buffer first, then the ranks below: rank-1 needs my chunk first
     return pa
 
 
@@ -400,7 +400,11 @@ class CpEngine:
             hl = plan.local_heads
             esz = q.element_size()
             sent = (self.world - 1) * 2 * B * hl * skv * D * esz + (self.ulysses - 1) * B * hl * sq * D * esz
-            ctas = max(16, min(64, (sent + (5 << 20) - 1) // (5 << 20)))
+            ctas = (sent + (5 << 20) - 1) // (5 << 20)
+            # SMs that the last, partly filled wave of the grid leaves idle can push for free
+            grid = ((sq + 255) // 256) * hl * B * self.ulysses
+            spare = (-grid) % 148
+            ctas = max(16, min(64, max(ctas, min(spare, 48))))
         wait_ns = config.cp.wait_limit_ns
         scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
         main = torch.cuda.current_stream(self.device)

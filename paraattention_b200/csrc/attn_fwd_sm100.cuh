@@ -237,13 +237,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // Fused exchange: the leading CTAs of the grid (always resident in the first wave, and
     // waiting for nobody) first store this rank's Q/K/V head-slices into the staging buffers
-    // of the ranks that consume them - own buffer first, then the peers in ring order - and
-    // only then take up their attention tiles. Every other CTA starts computing at once and
+    // of the ranks that consume them - own buffer first, then the ranks below in descending
+    // order (a consumer walks its chunks upwards from its own rank, so the first chunk it
+    // needs from a peer is the one that peer sends first) - and only then take up their
+    // attention tiles. Every other CTA starts computing at once and
     // meets a chunk only when it needs it.
     if (push.n_push_ctas > 0 && static_cast<int>(blockIdx.x) < push.n_push_ctas) {
         for (int di = 0; di < push.n_dest; ++di) {
-            int dest = push.first_dest + di;
-            if (dest >= push.n_dest) dest -= push.n_dest;
+            int dest = push.first_dest - di;
+            if (dest < 0) dest += push.n_dest;
             push_to_dest(push, dest, blockIdx.x, push.n_push_ctas);
         }
     }

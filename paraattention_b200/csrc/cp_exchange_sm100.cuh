@@ -16,7 +16,7 @@ struct PushParams {
     int n_jobs;
     uint32_t* flag[PA_MAX_CHUNKS];  // per destination, in that destination's memory
     int n_dest;
-    int first_dest;   // destinations are served in the order first_dest, first_dest+1, ... (mod n_dest)
+    int first_dest;   // destinations are served in the order first_dest, first_dest-1, ... (mod n_dest)
     int n_push_ctas;  // fused form only: how many leading CTAs of the attention grid push
 };
 
