@@ -149,15 +149,48 @@ def run_reference(args):
 # clocks
 # ------------------------------------------------------------------------------------------
 class ClockSampler:
+    """SM clock and slow-down reasons of one GPU, sampled every few milliseconds through NVML
+    from a thread of this process (a timed region of ten 1.6 ms steps is far shorter than
+    nvidia-smi's fastest loop); falls back to an `nvidia-smi -lms` child if NVML cannot be
+    loaded. Read-only queries."""
+
     Q = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NVML_REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
         self.lines = []
+        self.samples = []  # (time.time(), sm MHz, reasons bit mask)
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
 
     def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def loop():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append((time.time(), float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)),
+                                             int(reasons(h))))
+                    except pynvml.NVMLError:
+                        pass
+                    time.sleep(0.002)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+            return
+        except Exception:  # no NVML binding or no permission: use the command-line tool
+            self._thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"],
@@ -174,6 +207,16 @@ class ClockSampler:
         """Summarise the samples whose timestamps fall inside [t_begin, t_end] (time.time())."""
         import datetime
 
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            inside = [x for x in self.samples if t_begin is None or t_begin - 0.002 <= x[0] <= t_end + 0.002]
+            mask = 0
+            for x in inside:
+                mask |= x[2]
+            return {"sm_mhz": statistics.median([x[1] for x in inside]) if inside else None, "sm_max_mhz": self.max_mhz,
+                    "reasons": sorted(n for bit, n in self.NVML_REASONS.items() if mask & bit), "samples": len(inside),
+                    "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -198,9 +241,8 @@ class ClockSampler:
             for n, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(n)
-        load = sm
-        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 # ------------------------------------------------------------------------------------------
