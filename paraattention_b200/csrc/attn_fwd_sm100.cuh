@@ -207,8 +207,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem = ctl->tmem_base;
 
     // ---- which work unit: (batch, head, query chunk, pair of query tiles) -------------------
+    // The CTAs that push first (the leading ones of the grid) take the LAST work units: those
+    // belong to the query chunk that arrives last (and, in a causal run, to the short early
+    // tiles), so the units that can start at once go to CTAs that start at once.
     const int pairs_per_chunk = (p.q_rows + 2 * kTileM - 1) / (2 * kTileM);
     int unit = blockIdx.x;
+    if (push.n_push_ctas > 0) {
+        unit -= push.n_push_ctas;
+        if (unit < 0) unit += gridDim.x;
+    }
     int pair = unit % pairs_per_chunk;
     unit /= pairs_per_chunk;
     // the late query tiles of a causal run see the most keys: schedule them first
