@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this folder by running the ParaAttention reference itself.
 
-Run where the reference checkout is available (it is imported from ``--ref``, default
-``/root/reference/src``): CPU only, gloo, fp32 compute on bf16-representable inputs.
+Run where a checkout of the reference is available (it is imported from ``--ref``, the
+``src`` folder of that checkout): CPU only, gloo, fp32 compute on bf16-representable inputs.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [--ref <checkout>/src]      (from the repository root)
 
 Writes
   cp_attention_w2.npz   world 2: ulysses_attn_func, ring_attn_func (non-causal and causal)
@@ -219,9 +219,11 @@ def make_sparse_kv(ref: str):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference/src")
+    ap.add_argument("--ref", default=os.environ.get("PARA_ATTN_REF", "../reference/src"),
+                    help="src folder of a ParaAttention checkout")
     ap.add_argument("--only", choices=["attention", "fbcache", "sparse_kv"], default=None)
     args = ap.parse_args()
+    args.ref = os.path.abspath(args.ref)
     if args.only in (None, "attention"):
         make_attention(args.ref)
     if args.only in (None, "fbcache"):

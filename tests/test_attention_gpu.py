@@ -299,7 +299,7 @@ def test_merge_kernel_matches_oracle():
 
 
 def test_full_size_properties():
-    """At a BASELINE-sized shape (H=24, S=32760) a full fp32 reference is too much for a test;
+    """At the benchmark's shape (H=24, S=32760) a full fp32 reference is too much for a test;
     check sampled rows against the oracle and two size-independent properties."""
     H, S = 24, 32760
     q, k, v = seeded_qkv(1, H, S, S, seed=11, scale=0.5)
