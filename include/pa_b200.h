@@ -270,6 +270,26 @@ int pa_fbc_residual_diff_static(const void* h1, const void* h0, const void* prev
  * (utils.py:237-259) and the residual formation at utils.py:443-444. */
 int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t sub, int32_t dtype, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * TaylorSeer (src/para_attn/first_block_cache/taylorseer.py), the extrapolating variant of the
+ * cached residual. All tensors hold numel 16-bit elements (numel % 8 == 0, 16-byte aligned).
+ *
+ * pa_taylor_update: TaylorSeer.approximate_derivative (taylorseer.py:29-38) in one pass. y is
+ * d_0 of the step just computed, prev[i] the d_i of the previous computed step (i < depth), and
+ * cur[i] receives d_{i+1} = round(round(d_i - prev[i]) / window), chained in registers.
+ * depth <= 4; depth 0 does nothing.
+ *
+ * pa_taylor_approx: TaylorSeer.approximate_value (taylorseer.py:40-48): out = d[0] +
+ * sum_{i=1}^{terms-1} round(round(d[i] / i!) * elapsed^i) with the sum rounded after every
+ * term, as the chain of tensor operations rounds; terms <= 5. With add != NULL the kernel also
+ * performs the addition of apply_prev_hidden_states_residual (utils.py:238-243):
+ * out = round(that + add).
+ * ---------------------------------------------------------------------------------------- */
+int pa_taylor_update(const void* y, const void* const* prev, void* const* cur, int32_t depth, int32_t window,
+                     int64_t numel, int32_t dtype, void* stream);
+int pa_taylor_approx(const void* const* d, int32_t terms, int32_t elapsed, const void* add, void* out, int64_t numel,
+                     int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

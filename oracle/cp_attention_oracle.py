@@ -293,3 +293,66 @@ class FbcStateOracle:
         if not hit:
             self.prev[self._key()] = cur.copy()
         return hit
+
+
+# --------------------------------------------------------------------------------------
+# TaylorSeer (src/para_attn/first_block_cache/taylorseer.py:4-64)
+# --------------------------------------------------------------------------------------
+class TaylorSeerOracle:
+    """The reference's extrapolator on bf16 tensors, as arrays of bf16-representable fp32 values.
+
+    Every tensor operation of the reference produces a bf16 tensor, so every intermediate is
+    rounded: ``(d_i - prev_i)`` then ``/ window`` (taylorseer.py:35); ``(1 / i!) * d_i`` then
+    ``* elapsed**i`` then ``output += term`` (taylorseer.py:44-45). The scalars enter the
+    arithmetic as fp32, which is what a Python float against a bf16 tensor becomes.
+    """
+
+    def __init__(self, n_derivatives=2, warmup_steps=1, skip_interval_steps=1, compute_step_map=None):
+        self.n_derivatives = n_derivatives
+        self.order = n_derivatives + 1
+        self.warmup_steps = warmup_steps
+        self.skip_interval_steps = skip_interval_steps
+        self.compute_step_map = compute_step_map
+        self.prev = [None] * self.order
+        self.cur = [None] * self.order
+        self.current_step = -1
+        self.last_full = -1
+
+    def should_compute_full(self) -> bool:
+        s = self.current_step
+        if self.compute_step_map is not None:
+            return bool(self.compute_step_map[s])
+        return s < self.warmup_steps or (s - self.warmup_steps + 1) % self.skip_interval_steps == 0
+
+    def update(self, y: Array) -> None:
+        new = [None] * self.order
+        new[0] = np.asarray(y, dtype=np.float32)
+        window = np.float32(self.current_step - self.last_full)
+        for i in range(self.n_derivatives):
+            if self.cur[i] is not None and self.current_step > 1:
+                new[i + 1] = bf16_round(bf16_round(new[i] - self.cur[i]) / window)
+            else:
+                break
+        self.prev, self.cur = self.cur, new
+        self.last_full = self.current_step
+
+    def approximate_value(self) -> Array:
+        elapsed = self.current_step - self.last_full
+        out = None
+        for i, d in enumerate(self.cur):
+            if d is None:
+                break
+            if i == 0:
+                out = d.copy()  # 0 + (1.0 * d_0) * 1 is d_0 itself
+                continue
+            coef = np.float32(1.0 / math.factorial(i))
+            term = bf16_round(bf16_round(coef * d) * np.float32(elapsed ** i))
+            out = bf16_round(out + term)
+        return out
+
+    def step(self, y: Array) -> Array:
+        self.current_step += 1
+        if self.should_compute_full():
+            self.update(y)
+            return np.asarray(y, dtype=np.float32)
+        return self.approximate_value()

@@ -110,6 +110,12 @@ def load() -> C.CDLL:
     lib.pa_dbg_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pa_cp_attn_fwd.restype = C.c_int
     lib.pa_cp_attn_fwd.argtypes = [C.POINTER(CpAttnArgs), C.c_void_p]
+    lib.pa_taylor_update.restype = C.c_int
+    lib.pa_taylor_update.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int32, C.c_int32,
+                                     C.c_int64, C.c_int32, C.c_void_p]
+    lib.pa_taylor_approx.restype = C.c_int
+    lib.pa_taylor_approx.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int64,
+                                     C.c_int32, C.c_void_p]
     lib.pa_pack_key_mask.restype = C.c_int
     lib.pa_pack_key_mask.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
     lib.pa_cp_push.restype = C.c_int

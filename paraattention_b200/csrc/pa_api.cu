@@ -14,6 +14,7 @@
 #include "fbc_sm100.cuh"
 #include "key_mask_sm100.cuh"
 #include "merge_sm100.cuh"
+#include "taylor_sm100.cuh"
 
 namespace {
 
@@ -567,6 +568,83 @@ int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t 
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(PA_ECUDA, "axpy launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+namespace {
+int taylor_checks(const char* what, int64_t numel, int32_t dtype) {
+    if (numel <= 0 || numel % 8 != 0) return fail(PA_EINVAL, "%s: numel must be a positive multiple of 8", what);
+    if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "%s: dtype must be PA_BF16 or PA_F16", what);
+    return PA_OK;
+}
+bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+int taylor_blocks(long long n8) {
+    long long blocks = (n8 + pa::kFbcThreads - 1) / pa::kFbcThreads;
+    return int(blocks > 148 * 16 ? 148 * 16 : blocks);
+}
+}  // namespace
+
+int pa_taylor_update(const void* y, const void* const* prev, void* const* cur, int32_t depth, int32_t window,
+                     int64_t numel, int32_t dtype, void* stream) {
+    if (depth == 0) return PA_OK;  // nothing to derive yet
+    if (!y || !prev || !cur) return fail(PA_EINVAL, "taylor_update: NULL pointer");
+    if (depth < 0 || depth > pa::kTaylorMaxOrder - 1)
+        return fail(PA_EINVAL, "taylor_update: depth must be in [0, %d]", pa::kTaylorMaxOrder - 1);
+    if (window <= 0) return fail(PA_EINVAL, "taylor_update: window must be positive");
+    int rc = taylor_checks("taylor_update", numel, dtype);
+    if (rc != PA_OK) return rc;
+    pa::TaylorUpdateParams p;
+    memset(&p, 0, sizeof(p));
+    if (misaligned(y)) return fail(PA_EINVAL, "taylor_update: pointers must be 16-byte aligned");
+    p.y = static_cast<const uint4*>(y);
+    for (int i = 0; i < depth; ++i) {
+        if (!prev[i] || !cur[i]) return fail(PA_EINVAL, "taylor_update: prev[%d] / cur[%d] is NULL", i, i);
+        if (misaligned(prev[i]) || misaligned(cur[i])) return fail(PA_EINVAL, "taylor_update: pointers must be 16-byte aligned");
+        p.prev[i] = static_cast<const uint4*>(prev[i]);
+        p.cur[i] = static_cast<uint4*>(cur[i]);
+    }
+    p.depth = depth;
+    p.window = static_cast<float>(window);
+    p.n8 = numel / 8;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == PA_BF16) pa::taylor_update_kernel<true><<<taylor_blocks(p.n8), pa::kFbcThreads, 0, s>>>(p);
+    else pa::taylor_update_kernel<false><<<taylor_blocks(p.n8), pa::kFbcThreads, 0, s>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "taylor_update launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int pa_taylor_approx(const void* const* d, int32_t terms, int32_t elapsed, const void* add, void* out, int64_t numel,
+                     int32_t dtype, void* stream) {
+    if (!d || !out) return fail(PA_EINVAL, "taylor_approx: NULL pointer");
+    if (terms < 1 || terms > pa::kTaylorMaxOrder) return fail(PA_EINVAL, "taylor_approx: terms must be in [1, %d]", pa::kTaylorMaxOrder);
+    if (elapsed < 0) return fail(PA_EINVAL, "taylor_approx: elapsed must not be negative");
+    int rc = taylor_checks("taylor_approx", numel, dtype);
+    if (rc != PA_OK) return rc;
+    pa::TaylorApproxParams p;
+    memset(&p, 0, sizeof(p));
+    double fact = 1.0, pw = 1.0;
+    for (int i = 0; i < terms; ++i) {
+        if (!d[i]) return fail(PA_EINVAL, "taylor_approx: d[%d] is NULL", i);
+        if (misaligned(d[i])) return fail(PA_EINVAL, "taylor_approx: pointers must be 16-byte aligned");
+        p.d[i] = static_cast<const uint4*>(d[i]);
+        if (i > 0) {
+            fact *= i;
+            pw *= elapsed;
+        }
+        p.coef[i] = static_cast<float>(1.0 / fact);  // the scalar a tensor operation would see
+        p.power[i] = static_cast<float>(pw);
+    }
+    if (misaligned(out) || (add && misaligned(add))) return fail(PA_EINVAL, "taylor_approx: pointers must be 16-byte aligned");
+    p.terms = terms;
+    p.add = static_cast<const uint4*>(add);
+    p.out = static_cast<uint4*>(out);
+    p.n8 = numel / 8;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == PA_BF16) pa::taylor_approx_kernel<true><<<taylor_blocks(p.n8), pa::kFbcThreads, 0, s>>>(p);
+    else pa::taylor_approx_kernel<false><<<taylor_blocks(p.n8), pa::kFbcThreads, 0, s>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "taylor_approx launch: %s", cudaGetErrorString(e));
     return PA_OK;
 }
 

@@ -20,6 +20,7 @@ import torch
 
 from .. import _lib as L
 from .. import primitives as DP
+from .taylorseer import TaylorSeer
 
 _DTYPES = {torch.bfloat16: L.PA_BF16, torch.float16: L.PA_F16}
 
@@ -48,9 +49,14 @@ class CacheContext:
     executed_steps: int = 0
     is_alter_cache: bool = True
 
+    taylorseer: Optional[TaylorSeer] = None
+    alter_taylorseer: Optional[TaylorSeer] = None
+
     def __post_init__(self):
         if self.enable_taylorseer:
-            raise NotImplementedError("enable_taylorseer: TaylorSeer extrapolation is outside the accelerated path")
+            self.taylorseer = TaylorSeer(**self.taylorseer_kwargs)
+            if self.enable_alter_cache:
+                self.alter_taylorseer = TaylorSeer(**self.taylorseer_kwargs)
 
     def get_incremental_name(self, name=None):
         if name is None:
@@ -95,6 +101,13 @@ class CacheContext:
             self.is_alter_cache = not self.is_alter_cache
             if not self.is_alter_cache:
                 self.executed_steps += 1
+        if self.enable_taylorseer:
+            self.get_taylorseer().mark_step_begin()
+
+    def get_taylorseer(self):
+        if self.enable_alter_cache and self.is_alter_cache:
+            return self.alter_taylorseer
+        return self.taylorseer
 
     def is_slg_enabled(self):
         return self.slg_layers is not None
@@ -175,6 +188,10 @@ def mark_step_begin():
 
 def is_taylorseer_enabled():
     return _ctx().enable_taylorseer
+
+
+def get_taylorseer():
+    return _ctx().get_taylorseer()
 
 
 def is_slg_enabled():
@@ -282,6 +299,10 @@ def are_two_tensors_similar(t1, t2, *, threshold, parallelized=False):
 
 
 def apply_prev_hidden_states_residual(hidden_states, encoder_hidden_states=None):
+    if is_taylorseer_enabled():
+        # extrapolated residual + hidden states in one launch; the encoder states pass through
+        # unchanged (src/para_attn/first_block_cache/utils.py:238-243)
+        return get_taylorseer().approximate_value(add=hidden_states.contiguous()), encoder_hidden_states
     hidden_states_residual = get_hidden_states_residual()
     assert hidden_states_residual is not None, "hidden_states_residual must be set before"
     hidden_states = _axpy(hidden_states_residual, hidden_states.contiguous(), sub=False)
@@ -327,14 +348,21 @@ def get_first_hidden_states_residual():
 
 
 def set_hidden_states_residual(hidden_states_residual):
-    set_buffer("hidden_states_residual", hidden_states_residual)
+    if is_taylorseer_enabled():
+        get_taylorseer().update(hidden_states_residual)
+    else:
+        set_buffer("hidden_states_residual", hidden_states_residual)
 
 
 def get_hidden_states_residual():
+    if is_taylorseer_enabled():
+        return get_taylorseer().approximate_value()
     return get_buffer("hidden_states_residual")
 
 
 def set_encoder_hidden_states_residual(encoder_hidden_states_residual):
+    if is_taylorseer_enabled():
+        return
     set_buffer("encoder_hidden_states_residual", encoder_hidden_states_residual)
 
 

@@ -10,6 +10,7 @@ Writes
   cp_attention_w4.npz   world 4: UnifiedAttnMode on a 2x2 (ring x ulysses) mesh, RingAttnMode on 4
   fbcache_steps.npz     CachedTransformerBlocks decisions over a scripted bf16 sequence
   sparse_kv.npz         _attention_forward_sparse_kv (key-padding masks, batch 3) on one process
+  taylorseer.npz        TaylorSeer.step over a scripted bf16 sequence, three configurations
 
 The only change made to the reference is the rebinding of
 ``para_attn.ops._attention_forward_with_lse`` (which asserts CUDA tensors at
@@ -165,6 +166,8 @@ def make_fbcache(ref: str):
         "thr003_warm2": dict(residual_diff_threshold=0.03, warmup_steps=2),
         "thr02_ds2": dict(residual_diff_threshold=0.2, downsample_factor=2),
         "thr0": dict(residual_diff_threshold=0.0),
+        "thr008_taylor": dict(residual_diff_threshold=0.08, enable_taylorseer=True,
+                              taylorseer_kwargs=dict(n_derivatives=2)),
     }
     enc = torch.from_numpy(rng.standard_normal((1, 8, C)).astype(np.float32)).bfloat16()
     store = {"h0": np.stack([bits(x) for x in inputs]), "h1": np.stack([bits(x) for x in first_block_outputs]),
@@ -190,7 +193,7 @@ def make_fbcache(ref: str):
                 outs.append(bits(o))
                 enc_outs.append(bits(eo))
         store[f"{name}_hit"] = np.array(decisions)
-        if name in ("thr008", "thr02_ds2"):
+        if name in ("thr008", "thr02_ds2", "thr008_taylor"):
             store[f"{name}_out"] = np.stack(outs)
         if name == "thr008":
             store[f"{name}_enc_out"] = np.stack(enc_outs)
@@ -217,11 +220,35 @@ def make_sparse_kv(ref: str):
     print("sparse_kv", tuple(out.shape), "kept keys per batch element:", mask.sum(dim=-1).flatten().tolist())
 
 
+def make_taylorseer(ref: str):
+    """The reference's TaylorSeer class driven step by step with bf16 tensors on CPU."""
+    sys.path.insert(0, ref)
+    from para_attn.first_block_cache.taylorseer import TaylorSeer
+
+    T, N = 14, 512
+    rng = np.random.default_rng(11)
+    a, b, c = (rng.standard_normal(N).astype(np.float32) for _ in range(3))
+    ys = [torch.from_numpy(a + 0.07 * t * b + 0.004 * t * t * c).bfloat16() for t in range(T)]
+    store = {"y": np.stack([bits(y) for y in ys])}
+    cases = {
+        "d2_w1_s3": dict(n_derivatives=2, warmup_steps=1, skip_interval_steps=3),
+        "d3_w2_s4": dict(n_derivatives=3, warmup_steps=2, skip_interval_steps=4),
+        "d1_map": dict(n_derivatives=1, compute_step_map=[True, True, False, True, False, False, False, True, False,
+                                                          False, True, False, False, False]),
+    }
+    for name, kw in cases.items():
+        seer = TaylorSeer(**kw)
+        outs = [seer.step(y) for y in ys]
+        store[name] = np.stack([bits(o) for o in outs])
+        print(name, "computed steps:", [t for t in range(T) if seer.should_compute_full(t)])
+    np.savez_compressed(HERE / "taylorseer.npz", **store)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("PARA_ATTN_REF", "../reference/src"),
                     help="src folder of a ParaAttention checkout")
-    ap.add_argument("--only", choices=["attention", "fbcache", "sparse_kv"], default=None)
+    ap.add_argument("--only", choices=["attention", "fbcache", "sparse_kv", "taylorseer"], default=None)
     args = ap.parse_args()
     args.ref = os.path.abspath(args.ref)
     if args.only in (None, "attention"):
@@ -230,3 +257,5 @@ if __name__ == "__main__":
         make_fbcache(args.ref)
     if args.only in (None, "sparse_kv"):
         make_sparse_kv(args.ref)
+    if args.only in (None, "taylorseer"):
+        make_taylorseer(args.ref)

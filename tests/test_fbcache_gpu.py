@@ -1,6 +1,8 @@
 """First-Block-Cache kernels on the GPU against the oracle and the reference's recorded decisions."""
 import ctypes as C
 
+import math
+
 import numpy as np
 import pytest
 import torch
@@ -86,6 +88,7 @@ def test_axpy_bit_exact():
     ("thr003_warm2", dict(residual_diff_threshold=0.03, warmup_steps=2)),
     ("thr02_ds2", dict(residual_diff_threshold=0.2, downsample_factor=2)),
     ("thr0", dict(residual_diff_threshold=0.0)),
+    ("thr008_taylor", dict(residual_diff_threshold=0.08, enable_taylorseer=True, taylorseer_kwargs=dict(n_derivatives=2))),
 ])
 def test_cached_blocks_follow_reference_step_by_step(golden_dir, case, kw):
     """Same scripted sequence as tests/golden/make_golden.py: the skip/compute decision and the
@@ -138,3 +141,57 @@ def test_full_size_sums_and_bandwidth_shape():
     sp = prev.abs().double().sum().item()
     np.testing.assert_allclose(res[0], sd, rtol=1e-5)
     np.testing.assert_allclose(res[1], sp, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case,kw", [
+    ("d2_w1_s3", dict(n_derivatives=2, warmup_steps=1, skip_interval_steps=3)),
+    ("d3_w2_s4", dict(n_derivatives=3, warmup_steps=2, skip_interval_steps=4)),
+    ("d1_map", dict(n_derivatives=1, compute_step_map=[True, True, False, True, False, False, False, True, False,
+                                                       False, True, False, False, False])),
+])
+def test_taylorseer_kernels_bit_exact(golden_dir, case, kw, dtype):
+    """TaylorSeer.step on the GPU: for bf16 against the reference's own outputs (fixture), for
+    fp16 against the same chain of tensor operations done by ATen on the GPU."""
+    from paraattention_b200.first_block_cache.taylorseer import TaylorSeer
+
+    g = np.load(golden_dir / "taylorseer.npz")
+    ys = bf16_from_bits(g["y"]).to(dtype)
+    seer = TaylorSeer(**kw)
+    prev, cur, last = None, None, -1
+    for t in range(ys.shape[0]):
+        got = seer.step(ys[t])
+        if dtype == torch.bfloat16:
+            assert torch.equal(got, bf16_from_bits(g[case][t])), f"{case}: step {t} differs from the reference"
+        # the same arithmetic as separate tensor operations (true division, as on the CPU)
+        if seer.last_non_approximated_step == t:
+            new = [ys[t]]
+            if t > 1 and cur is not None:
+                for i in range(seer.n_derivatives):
+                    if i < len(cur):
+                        new.append(torch.true_divide(new[i] - cur[i], torch.tensor(float(t - last), device="cuda")).to(dtype))
+            prev, cur, last = cur, new, t
+            want = ys[t]
+        else:
+            want = cur[0]
+            for i in range(1, len(cur)):
+                want = want + (1 / math.factorial(i)) * cur[i] * ((t - last) ** i)
+        assert torch.equal(got, want), f"{case} {dtype}: step {t} differs from the chained tensor operations"
+
+
+def test_taylorseer_fused_add_and_refusals():
+    from paraattention_b200.first_block_cache.taylorseer import TaylorSeer
+
+    g = torch.Generator().manual_seed(0)
+    ys = [torch.randn(4, 64, generator=g).bfloat16().cuda() for _ in range(4)]
+    h = torch.randn(4, 64, generator=g).bfloat16().cuda()
+    seer = TaylorSeer(n_derivatives=2, warmup_steps=3, skip_interval_steps=10)
+    for y in ys[:3]:
+        seer.step(y)
+    seer.mark_step_begin()
+    plain = seer.approximate_value()
+    assert torch.equal(seer.approximate_value(add=h), plain + h)
+    with pytest.raises(NotImplementedError):
+        seer.update(torch.zeros(3, 5, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(NotImplementedError):
+        seer.update(torch.zeros(4, 64, dtype=torch.float32, device="cuda"))

@@ -174,7 +174,17 @@ def test_cache_context_step_bookkeeping():
                      ctx.slg_should_skip_block(1)))
     assert seen == [(False, 1, 0.1, False), (True, 1, 0.3, True), (False, 2, 0.1, False), (True, 2, 0.3, True)]
     assert set(ctx.buffers) == {"x", "x_alter"}
+    # TaylorSeer: one extrapolator per cache (main / alter), stepped with the cache it belongs to
+    ctx = fbc.create_cache_context(enable_taylorseer=True, enable_alter_cache=True,
+                                   taylorseer_kwargs=dict(n_derivatives=3, warmup_steps=2, skip_interval_steps=3))
+    for _ in range(3):
+        ctx.mark_step_begin()
+    assert (ctx.taylorseer.current_step, ctx.alter_taylorseer.current_step) == (1, 0)
+    assert ctx.get_taylorseer() is ctx.taylorseer and ctx.taylorseer.ORDER == 4
+    assert [ctx.taylorseer.should_compute_full(s) for s in range(8)] == [True, True, False, False, True, False, False, True]
     with pytest.raises(NotImplementedError):
-        fbc.create_cache_context(enable_taylorseer=True)
+        fbc.create_cache_context(enable_taylorseer=True, taylorseer_kwargs=dict(n_derivatives=9))
+    with pytest.raises(RuntimeError):
+        ctx.taylorseer.update(torch.zeros(8, dtype=torch.bfloat16))  # CPU tensor: no CPU path
     with pytest.raises(AssertionError):
         fbc.mark_step_begin()

@@ -126,3 +126,19 @@ def test_key_mask_against_reference_sparse_kv(golden_dir):
     none = np.zeros_like(mask)
     out0, lse0 = O.sdpa_with_lse(q, k, v, key_mask=none)
     assert (out0 == 0).all() and np.isneginf(lse0).all()
+
+
+@pytest.mark.parametrize("case,kw", [
+    ("d2_w1_s3", dict(n_derivatives=2, warmup_steps=1, skip_interval_steps=3)),
+    ("d3_w2_s4", dict(n_derivatives=3, warmup_steps=2, skip_interval_steps=4)),
+    ("d1_map", dict(n_derivatives=1, compute_step_map=[True, True, False, True, False, False, False, True, False,
+                                                       False, True, False, False, False])),
+])
+def test_taylorseer_bit_exact_against_reference(golden_dir, case, kw):
+    """TaylorSeerOracle.step against the reference's TaylorSeer.step on bf16 tensors, bit for bit."""
+    g = np.load(golden_dir / "taylorseer.npz")
+    ys = _f32(g["y"])
+    seer = O.TaylorSeerOracle(**kw)
+    for t in range(ys.shape[0]):
+        got = seer.step(ys[t])
+        assert np.array_equal(got, _f32(g[case][t])), f"{case}: step {t} differs"
