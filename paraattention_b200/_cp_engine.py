@@ -484,6 +484,25 @@ def get_engine(flat_group: dist.ProcessGroup, ulysses: int, ring: int, u: int, r
     return eng
 
 
+_engine_list: List[CpEngine] = []
+
+
+def engine_id(flat_group: dist.ProcessGroup, ulysses: int, ring: int, u: int, r: int, device_index: int) -> int:
+    """A small integer standing for the engine of this (group, mesh position, device): what the
+    ``para_attn::cp_attention_forward`` custom op carries instead of Python objects, so that
+    a tracing compiler sees a constant. Creating an engine is collective over the group."""
+    eng = get_engine(flat_group, ulysses, ring, u, r, torch.device("cuda", device_index))
+    for i, e in enumerate(_engine_list):
+        if e is eng:
+            return i
+    _engine_list.append(eng)
+    return len(_engine_list) - 1
+
+
+def engine_by_id(i: int) -> CpEngine:
+    return _engine_list[i]
+
+
 def check_device_status() -> None:
     """Raise if any context-parallel kernel reported a timed-out wait (synchronises)."""
     for eng in _engines.values():

@@ -21,6 +21,7 @@ __all__ = [
     "attention_forward_with_lse",
     "attention_forward",
     "attention_forward_sparse_kv",
+    "cp_attention_forward",
     "key_mask_of",
     "pack_key_mask",
     "merge_out_lse_",
@@ -188,6 +189,33 @@ def attention_forward_sparse_kv(
 
 @torch.library.register_fake("para_attn::attention_forward_sparse_kv")
 def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None):
+    B, H, Sq, D = query.shape
+    return query.new_empty((B, Sq, H, D)).transpose(1, 2)
+
+
+@torch.library.custom_op("para_attn::cp_attention_forward", mutates_args=(), device_types=("cuda",))
+def cp_attention_forward(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    key_mask: Optional[torch.Tensor],
+    is_causal: bool,
+    scale: Optional[float],
+    engine_id: int,
+) -> torch.Tensor:
+    """One context-parallel attention call of this rank (exchange + chunked attention + output
+    scatter) as a custom op, so that the Ring / Ulysses / Unified modes stay traceable: the
+    engine (process group, mesh position, workspace) is named by an integer
+    (``_cp_engine.engine_id``). No counterpart in the reference, whose collectives are traceable
+    functional collectives (src/para_attn/primitives.py:72-78)."""
+    from . import _cp_engine
+
+    return _cp_engine.engine_by_id(engine_id).attention(query, key, value, scale, is_causal=is_causal,
+                                                         key_mask=key_mask)
+
+
+@torch.library.register_fake("para_attn::cp_attention_forward")
+def _(query, key, value, key_mask, is_causal, scale, engine_id):
     B, H, Sq, D = query.shape
     return query.new_empty((B, Sq, H, D)).transpose(1, 2)
 

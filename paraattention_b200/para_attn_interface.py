@@ -71,16 +71,21 @@ def _local_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal
         query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale)
 
 
+@torch.compiler.assume_constant_result
+def _engine_id(flat_group, ulysses, ring, u, r, device_index):
+    return _cp_engine.engine_id(flat_group, ulysses, ring, u, r, device_index)
+
+
 def _cp_attention(query, key, value, scale, *, flat_group, ulysses, ring, u, r, is_causal=False, attn_mask=None):
-    assert query.device.type == "cuda", "Must be CUDA tensors"
-    eng = _cp_engine.get_engine(flat_group, ulysses, ring, u, r, query.device)
+    # (CPU tensors never get here: _require_kernel refuses them, and the op below is CUDA-only)
+    eid = _engine_id(flat_group, ulysses, ring, u, r, query.device.index)
     key_mask = None
     if attn_mask is not None:
         # keys of all ranks, chunk by chunk in flat-rank order: for a Ulysses group that is the
         # order its all-to-all produces (src/para_attn/para_attn_interface.py:60-72), the layout
         # the reference's adapters build their masks in
         key_mask = para_attn_ops.key_mask_of(attn_mask, query.shape[0], ulysses * ring * key.shape[2])
-    return eng.attention(query, key, value, scale, is_causal=bool(is_causal), key_mask=key_mask)
+    return para_attn_ops.cp_attention_forward(query, key, value, key_mask, bool(is_causal), scale, eid)
 
 
 def _require_kernel(query, key, value, attn_mask, dropout_p, is_causal, what, world=1):

@@ -10,6 +10,7 @@ def torch_version_check(op, v):
     return getattr(version.parse(torch.__version__), op)(version.parse(v))
 
 
+@torch.compiler.assume_constant_result
 def get_force_dispatch_to_custom_ops():
     return config.attention.force_dispatch_to_custom_ops
 

@@ -214,6 +214,16 @@ def _mp_worker(rank, world, port, mode, ret):
             mask = (torch.rand(1, 1, 1, S, generator=torch.Generator().manual_seed(5)) < 0.6).cuda()
             fn = pa.ulysses_attn_func if mode == "ulysses_mask" else pa.ring_attn_func
             out = fn(qs, ks, vs, attn_mask=mask)
+        elif mode == "compiled_ulysses_causal":
+            if rep == 0:
+                attn_mode = pa.UlyssesAttnMode()
+
+                def fn(a, b, c):
+                    with attn_mode:
+                        return torch.nn.functional.scaled_dot_product_attention(a, b, c, is_causal=True)
+
+                compiled = torch.compile(fn, fullgraph=True, backend="aot_eager")
+            out = compiled(qs, ks, vs)
         elif mode == "ring_d64_causal":
             with pa.RingAttnMode():
                 out = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True)
@@ -237,7 +247,7 @@ def _mp_worker(rank, world, port, mode, ret):
 
 
 @pytest.mark.parametrize("mode", ["ulysses", "ring", "unified", "ring_causal", "ulysses_causal", "ring_d64_causal",
-                                  "ulysses_d64", "ulysses_mask", "ring_mask"])
+                                  "ulysses_d64", "ulysses_mask", "ring_mask", "compiled_ulysses_causal"])
 def test_multi_gpu_processes(mode):
     n = torch.cuda.device_count()
     if n < 2:
@@ -250,7 +260,8 @@ def test_multi_gpu_processes(mode):
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
     port = 29700 + {"ulysses": 1, "ring": 2, "unified": 3, "ring_causal": 4, "ulysses_causal": 5, "ring_d64_causal": 6,
-                    "ulysses_d64": 7, "ulysses_mask": 8, "ring_mask": 9}[mode]
+                    "ulysses_d64": 7, "ulysses_mask": 8, "ring_mask": 9,
+                    "compiled_ulysses_causal": 10}[mode]
     procs = [ctx.Process(target=_mp_worker, args=(r, world, port, mode, ret)) for r in range(world)]
     for p in procs:
         p.start()

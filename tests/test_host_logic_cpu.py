@@ -188,3 +188,65 @@ def test_cache_context_step_bookkeeping():
         ctx.taylorseer.update(torch.zeros(8, dtype=torch.bfloat16))  # CPU tensor: no CPU path
     with pytest.raises(AssertionError):
         fbc.mark_step_begin()
+
+
+def _trace_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import paraattention_b200 as pa
+    from paraattention_b200 import _cp_engine as E
+    from paraattention_b200 import para_attn_interface as I
+
+    # Tracing only: stand-ins let CPU tensors reach the context-parallel custom op, which is
+    # CUDA-only, so running the traced graph must fail in the op and nowhere before it.
+    I._kernel_can_run = lambda *a, **k: True
+    E.get_engine = lambda group, U, R, u, r, device: ("engine", U, R, u, r)
+    q = torch.randn(1, 2, 16, 128)
+    mesh = dist.init_device_mesh("cpu", (1, 2), mesh_dim_names=("ring", "ulysses"))
+    report = {}
+    for name, mode in (("ulysses", pa.UlyssesAttnMode()), ("ring", pa.RingAttnMode()), ("unified", pa.UnifiedAttnMode(mesh))):
+        graphs = []
+
+        def backend(gm, inputs):
+            graphs.append([str(n.target) for n in gm.graph.nodes if n.op == "call_function"])
+            return gm.forward
+
+        def fn(q, k, v):
+            with mode:
+                return F.scaled_dot_product_attention(q, k, v, is_causal=True)
+
+        torch._dynamo.reset()
+        try:
+            torch.compile(fn, fullgraph=True, backend=backend)(q, q, q)
+            err = "ran on CPU"
+        except NotImplementedError as e:
+            err = "op refused CPU" if "cp_attention_forward" in str(e) else f"NotImplementedError: {e}"
+        except Exception as e:  # a tracing failure would land here
+            err = f"{type(e).__name__}: {str(e)[:200]}"
+        report[name] = (graphs, err)
+    if rank == 0:
+        ret.put(report)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_modes_trace_into_one_custom_op_with_fullgraph():
+    """torch.compile(fullgraph=True) around `with <Mode>: F.scaled_dot_product_attention(...)` (the
+    reference's tests/test_interface.py:97-98) must trace, on every rank, into a single graph whose
+    only call is the context-parallel custom op."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_trace_worker, args=(r, 2, 29655, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    report = ret.get(timeout=600)
+    for p in procs:
+        p.join(timeout=60)
+    for name, (graphs, err) in report.items():
+        assert graphs == [["para_attn.cp_attention_forward.default"]], f"{name}: traced graphs {graphs} ({err})"
+        assert err == "op refused CPU", f"{name}: {err}"
