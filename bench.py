@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--heads", type=int, default=24)
     ap.add_argument("--seq", type=int, default=32760)
     ap.add_argument("--mesh", default=None, help="UxR, default Nx1 (all Ulysses)")
-    ap.add_argument("--workload", default="attention", choices=["attention", "flux", "wan", "hunyuan"],
+    ap.add_argument("--workload", default="attention", choices=["attention", "flux", "wan", "hunyuan", "fbcache"],
                     help="attention = the headline op benchmark; the others time one transformer forward")
     ap.add_argument("--layers", type=int, default=None, help="DiT workloads: override the block count (quick runs)")
     ap.add_argument("--fbcache", type=float, default=0.0, help="DiT workloads: First-Block-Cache threshold (0 = off)")
@@ -509,11 +509,81 @@ def run_dit(args):
     dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------
+# third leg: the HBM-bound cache kernels against the measured copy bandwidth
+# ------------------------------------------------------------------------------------------
+def run_fbcache_kernels(args):
+    """--workload fbcache: GB/s of the First-Block-Cache kernels on a Wan-2.1-sized residual
+    (32760 tokens x 5120 channels, bf16: 335 MB per tensor, larger than L2), one JSON line per
+    kernel. Algorithmic bytes: decision kernel 3 reads + 1 write; TaylorSeer update (2
+    derivatives) 3 reads + 2 writes; TaylorSeer extrapolation + add 4 reads + 1 write."""
+    import torch
+
+    from paraattention_b200.first_block_cache import utils as fbc
+    from paraattention_b200.first_block_cache.taylorseer import TaylorSeer
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows, cols = 32760, 5120
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda: torch.randn(1, rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16()  # noqa: E731
+    h0, h1, prev = mk(), mk(), mk()
+    tensor_bytes = h0.numel() * 2
+    seer = TaylorSeer(n_derivatives=2, warmup_steps=100)
+    for _ in range(3):  # three computed steps: two derivatives exist from here on
+        seer.step(mk())
+    y = mk()
+    peaks = load_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        evs = []
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in evs) / args.steps
+
+    def taylor_update():
+        seer.current_step += 1
+        seer.update(y)
+
+    legs = [
+        ("fbc_residual_diff_kernel", 4, lambda: fbc.fused_residual_diff(h1, h0, prev)),
+        ("taylor_update_kernel", 5, taylor_update),
+        ("taylor_approx_kernel", 5, lambda: seer.approximate_value(add=h0)),
+    ]
+    begin = time.time()
+    results = [(name, n, timed(fn)) for name, n, fn in legs]
+    clocks = sampler.stop(begin, time.time())
+    for name, n_tensors, ms in results:
+        gbs = n_tensors * tensor_bytes / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "fbcache_kernel_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{name}: residual of {rows} tokens x {cols} channels",
+                       "l2": f"{n_tensors} tensors of {tensor_bytes >> 20} MB per launch, larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": f"{peaks['source']} copy bandwidth",
+                         "kernel": name, "bytes_per_launch": n_tensors * tensor_bytes},
+            "clocks": clocks, "gpu_launches": args.steps,
+        }), flush=True)
+
+
 if __name__ == "__main__":
     a = parse_args()
     VARIANT["D"], VARIANT["causal"] = a.head_dim, a.causal
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "fbcache":
+        run_fbcache_kernels(a)
     elif a.workload != "attention":
         run_dit(a)
     else:

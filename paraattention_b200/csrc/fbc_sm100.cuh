@@ -108,7 +108,7 @@ fbc_residual_diff_kernel(const uint4* __restrict__ h1, const uint4* __restrict__
     float acc_d = 0.f, acc_p = 0.f;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
-        const uint4 a = __ldcs(h1 + i), b = __ldcs(h0 + i);
+        const uint4 a = __ldg(h1 + i), b = __ldg(h0 + i);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
         uint32_t cw[4];
         float cur[8];
@@ -119,7 +119,7 @@ fbc_residual_diff_kernel(const uint4* __restrict__ h1, const uint4* __restrict__
             cw[k] = pack16<kBF16>(cur[2 * k], cur[2 * k + 1]);
         }
         if (prev != nullptr) {
-            const uint4 p = __ldcs(prev + i);
+            const uint4 p = __ldg(prev + i);
             const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
 #pragma unroll
             for (int k = 0; k < 4; ++k) {

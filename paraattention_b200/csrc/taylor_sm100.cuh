@@ -17,6 +17,20 @@ namespace pa {
 
 constexpr int kTaylorMaxOrder = 5;  // d_0 .. d_4
 
+// a / w rounded to nearest (the value of an IEEE division) without the general division
+// sequence: w is a small positive integer whose reciprocal rw is correctly rounded, so two
+// residual corrections of a * rw land on the correctly rounded quotient; operands outside a
+// comfortable range take the IEEE path.
+__device__ __forceinline__ float div_rn_by_small(float a, float w, float rw) {
+    const float mag = fabsf(a);
+    if (a != 0.0f && !(mag > 1e-30f && mag < 1e30f)) return __fdiv_rn(a, w);
+    float q = a * rw;
+    float r = __fmaf_rn(-q, w, a);
+    q = __fmaf_rn(r, rw, q);
+    r = __fmaf_rn(-q, w, a);
+    return __fmaf_rn(r, rw, q);
+}
+
 struct TaylorUpdateParams {
     const uint4* y;                          // d_0 of this step
     const uint4* prev[kTaylorMaxOrder - 1];  // d_0 .. d_{depth-1} of the previous computed step
@@ -30,22 +44,27 @@ template <bool kBF16>
 __global__ void __launch_bounds__(kFbcThreads)
 taylor_update_kernel(const __grid_constant__ TaylorUpdateParams p) {
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const float rw = __frcp_rn(p.window);
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n8; i += stride) {
+        // all loads first: the stores below must not hold back the later loads
         uint4 d = __ldg(p.y + i);
+        uint4 pv[kTaylorMaxOrder - 1];
+#pragma unroll
+        for (int k = 0; k < kTaylorMaxOrder - 1; ++k)
+            if (k < p.depth) pv[k] = __ldg(p.prev[k] + i);
         uint32_t* dw = reinterpret_cast<uint32_t*>(&d);
 #pragma unroll
         for (int k = 0; k < kTaylorMaxOrder - 1; ++k) {
             if (k < p.depth) {
-                const uint4 pv = __ldg(p.prev[k] + i);
-                const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pv);
+                const uint32_t* pw = reinterpret_cast<const uint32_t*>(&pv[k]);
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     // (d - prev) is a tensor of the 16-bit type, so is the quotient
                     const float lo = round16<kBF16>(lo16<kBF16>(dw[w]) - lo16<kBF16>(pw[w]));
                     const float hi = round16<kBF16>(hi16<kBF16>(dw[w]) - hi16<kBF16>(pw[w]));
-                    dw[w] = pack16<kBF16>(__fdiv_rn(lo, p.window), __fdiv_rn(hi, p.window));
+                    dw[w] = pack16<kBF16>(div_rn_by_small(lo, p.window, rw), div_rn_by_small(hi, p.window, rw));
                 }
-                p.cur[k][i] = d;
+                __stcs(p.cur[k] + i, d);  // streaming store: not read again by this kernel
             }
         }
     }
@@ -101,7 +120,7 @@ taylor_approx_kernel(const __grid_constant__ TaylorApproxParams p) {
 #pragma unroll
             for (int w = 0; w < 4; ++w) ow[w] = pack16<kBF16>(acc[2 * w], acc[2 * w + 1]);
         }
-        p.out[i] = o;
+        __stcs(p.out + i, o);  // streaming store: not read again by this kernel
     }
 }
 
