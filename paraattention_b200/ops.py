@@ -193,7 +193,10 @@ def _(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scal
     return query.new_empty((B, Sq, H, D)).transpose(1, 2)
 
 
-@torch.library.custom_op("para_attn::cp_attention_forward", mutates_args=(), device_types=("cuda",))
+# (the expected values of the exchange counters advance on the host with every call, so a
+# replayed CUDA graph of this op would wait for counts that never come: tagged accordingly)
+@torch.library.custom_op("para_attn::cp_attention_forward", mutates_args=(), device_types=("cuda",),
+                         tags=(torch.Tag.cudagraph_unsafe,))
 def cp_attention_forward(
     query: torch.Tensor,
     key: torch.Tensor,
