@@ -184,15 +184,6 @@ def _fix(x: torch.Tensor) -> torch.Tensor:
     return x if ok else x.contiguous()
 
 
-def launch_push(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int, stream: int) -> None:
-    """Stand-alone pa_cp_push of this rank's shard into every consumer's staging buffer
-    (parity ``par``). Multi-GPU runs use the fused form instead (``build_push_args`` handed
-    to ``launch_attention``); this one serves one-GPU emulation, where all pushes must be
-    complete before any attention launch starts."""
-    pa = build_push_args(plan, ws, par, q, k, v, ctas)
-    L.check(L.load().pa_cp_push(C.byref(pa), stream))
-
-
 def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int,
                     skip_self: bool = True) -> "L.CpPushArgs":
     """Describe the pushes of this rank: which head-slice of q/k/v goes to which rank's buffer.

@@ -3,7 +3,7 @@
 ``attention.force_dispatch_to_custom_ops``: in the reference it routes the final,
 non-parallel SDPA of ``UnifiedAttnMode`` through the custom op instead of
 ``F.scaled_dot_product_attention``. Here the custom op *is* the product path, so the CUDA
-bf16/f16 head_dim-128 case always goes to it; the flag additionally makes unsupported
+bf16/f16 head_dim 64 / 128 case always goes to it; the flag additionally makes unsupported
 inputs raise instead of being handed back to PyTorch's own SDPA.
 
 ``attention.allow_reduced_precision_compute``: the reference lets torch's ring merger run in

@@ -4,11 +4,12 @@
 // tile of 128 rows. Warp roles (20 warps):
 //   warps 0-15  softmax. Warp w serves TMEM lane quarter w%4 (32 query rows) of query tile
 //               (w/4)%2 and key-column half w/8: two threads share a query row, each owns
-//               64 of the tile's 128 key columns (and, in the epilogue, 64 of O's columns).
+//               64 of the tile's 128 key columns (and, in the epilogue, half of O's columns).
 //   warp  16    MMA issuer (one thread): S_t = Q_t K_j^T into TMEM, O_t += P_t V_j from TMEM
 //   warp  17    TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
 //   warps 18-19 idle; they complete the control warpgroup that gives registers away
-// TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512);
+// TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512) for
+// head_dim 128 (O0 [256,320) O1 [320,384) for head_dim 64);
 // P_t (bf16/f16) overwrites S_t in place - each thread packs its 64 probabilities into the
 // first 32 of its own 64 logit columns - and is the TMEM A operand of P V.
 // While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs; the
@@ -17,6 +18,9 @@
 //
 // In context-parallel runs the same launch also performs the exchange (see the fused push
 // below): one kernel per attention call and rank, no collective library call on the path.
+//
+// Template parameters select bf16 / f16, head_dim 64 / 128 and causal masking; a key-padding
+// mask is a run-time option (one 64-bit word of key flags per half tile).
 //
 // Key/value rows come as a list of equally sized chunks (one per source rank in context
 // parallel runs, one in total otherwise); running max / sum / O stay on chip across
