@@ -79,3 +79,31 @@ def test_ops_refuse_cpu_tensors():
         ops.attention_forward(q, q, q)
     with pytest.raises(RuntimeError):
         fbc.fused_residual_diff(q, q, None)
+
+
+def test_new_entry_points_validate_without_a_device(lib):
+    """pa_pack_key_mask, pa_taylor_update and pa_taylor_approx refuse bad arguments before any
+    launch (no GPU is touched on these paths)."""
+    from paraattention_b200 import _lib as L
+
+    assert lib.pa_pack_key_mask(None, 8, 1, 1, 8, None, None) == L.PA_EINVAL
+    buf = (C.c_uint8 * 64)()
+    out = (C.c_uint64 * 4)()
+    addr, oaddr = C.addressof(buf), C.addressof(out)
+    assert lib.pa_pack_key_mask(addr, 4, 1, 1, 8, oaddr, None) == L.PA_EINVAL      # stride shorter than the keys
+    assert lib.pa_pack_key_mask(addr, 8, 0, 1, 8, oaddr, None) == L.PA_EINVAL      # empty batch
+    ptrs = (C.c_void_p * 4)()
+    assert lib.pa_taylor_update(addr, ptrs, ptrs, 0, 1, 64, L.PA_BF16, None) == L.PA_OK  # depth 0: nothing to do
+    assert lib.pa_taylor_update(addr, ptrs, ptrs, 5, 1, 64, L.PA_BF16, None) == L.PA_EINVAL
+    assert lib.pa_taylor_update(addr, ptrs, ptrs, 1, 0, 64, L.PA_BF16, None) == L.PA_EINVAL
+    assert lib.pa_taylor_update(addr, ptrs, ptrs, 1, 1, 63, L.PA_BF16, None) == L.PA_EINVAL
+    assert lib.pa_taylor_update(addr, ptrs, ptrs, 1, 1, 64, L.PA_BF16, None) == L.PA_EINVAL  # NULL prev[0]
+    assert lib.pa_taylor_approx(ptrs, 0, 1, None, addr, 64, L.PA_BF16, None) == L.PA_EINVAL
+    assert lib.pa_taylor_approx(ptrs, 6, 1, None, addr, 64, L.PA_BF16, None) == L.PA_EINVAL
+    assert lib.pa_taylor_approx(ptrs, 1, -1, None, addr, 64, L.PA_BF16, None) == L.PA_EINVAL
+    assert lib.pa_taylor_approx(ptrs, 1, 1, None, addr, 64, 7, None) == L.PA_EINVAL
+    a = L.AttnArgs()
+    a.q = a.k = a.v = a.out = addr
+    a.batch = a.heads = a.seq_q = a.seq_kv = 1
+    a.head_dim, a.scale = 96, 1.0
+    assert lib.pa_attn_fwd(C.byref(a), None) == L.PA_ENOTSUP and b"64 and 128" in lib.pa_last_error()

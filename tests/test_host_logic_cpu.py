@@ -250,3 +250,54 @@ def test_modes_trace_into_one_custom_op_with_fullgraph():
     for name, (graphs, err) in report.items():
         assert graphs == [["para_attn.cp_attention_forward.default"]], f"{name}: traced graphs {graphs} ({err})"
         assert err == "op refused CPU", f"{name}: {err}"
+
+
+def test_key_mask_of_accepts_only_key_padding_masks():
+    from paraattention_b200.ops import key_mask_of
+
+    m = torch.rand(2, 1, 1, 10) < 0.5
+    assert torch.equal(key_mask_of(m, 2, 10), m[:, 0, 0, :])
+    assert torch.equal(key_mask_of(m[:1], 2, 10), m[:1, 0, 0, :].expand(2, 10))   # batch broadcast
+    assert torch.equal(key_mask_of(m[0, 0, 0], 2, 10), m[0, 0, 0].expand(2, 10))  # 1-D mask
+    assert key_mask_of(None, 2, 10) is None
+    assert key_mask_of(m.float(), 2, 10) is None                     # additive masks are not key masks
+    assert key_mask_of(m.expand(2, 4, 1, 10), 2, 10) is None         # per-head
+    assert key_mask_of(m.expand(2, 1, 7, 10), 2, 10) is None         # per-query
+    assert key_mask_of(m, 2, 11) is None and key_mask_of(m, 3, 10) is None
+
+
+def test_causal_positions_and_mask_words_in_the_launch_arguments():
+    """Chunk c of the sequence sits at c * rows, c = ring index * U + ulysses index: the order
+    of the Ulysses all-to-all and of causal ring attention alike."""
+    from paraattention_b200 import _cp_engine as E
+
+    U, R, H, sq, D = 2, 3, 4, 100, 64
+    plan = E.CpPlan(U, R, 1, 2, H)  # u = 1, r = 2 -> flat rank 5
+    layout = E._make_layout(U * R, U, *E.stage_sizes(plan, 1, sq, sq, D, 2))
+    buf = torch.zeros(layout.total, dtype=torch.uint8)
+    ws = E.Workspace(layout, buf, [buf.data_ptr()] * (U * R), plan.rank)
+    a = E.build_attention_args(plan, ws, 0, (1, H, sq, D), torch.bfloat16, sq, 0.125, 7, 1000, None, is_causal=True)
+    assert a.is_causal == 1 and a.head_dim == D and a.heads == H // U
+    assert (a.n_q_chunks, a.q_first, a.n_kv_chunks, a.kv_first) == (U, 1, U * R, 5)
+    assert list(a.q_pos)[:U] == [4 * sq, 5 * sq]
+    assert list(a.kv_pos)[:U * R] == [c * sq for c in range(U * R)]
+    assert a.key_bits is None
+    plain = E.build_attention_args(plan, ws, 0, (1, H, sq, D), torch.bfloat16, sq, 0.125, 7, 1000, None)
+    assert plain.is_causal == 0 and list(plain.q_pos) == [0] * 8
+    bits = torch.zeros(1, U * R, 2, dtype=torch.int64)
+    masked = E.build_attention_args(plan, ws, 0, (1, H, sq, D), torch.bfloat16, sq, 0.125, 7, 1000, None, key_bits=bits)
+    assert masked.key_bits == bits.data_ptr()
+    jobs = E.build_push_args(plan, ws, 0, *(torch.zeros(1, H, sq, D, dtype=torch.bfloat16),) * 3, 4)
+    assert {jobs.jobs[i].head_dim for i in range(jobs.n_jobs)} == {D} and jobs.first_dest == plan.rank
+
+
+def test_host_pipeline_group_choice():
+    from paraattention_b200.host_io import _default_groups
+
+    assert _default_groups(24, 32760, 1, 1, 1) == 12     # one GPU: launches overlap, 1.5 waves are enough
+    assert _default_groups(24, 16380, 1, 2, 2) == 3      # two ranks: groups of 8 heads, three waves each
+    assert _default_groups(24, 4095, 1, 8, 8) == 1       # eight ranks: three heads per rank, nothing to split
+    assert _default_groups(24, 4608, 1, 1, 1) == 1       # small problem: one launch
+    for heads, U in ((24, 2), (40, 8), (6, 3)):
+        g = _default_groups(heads, 20000, 1, U, U)
+        assert heads % g == 0 and (heads // g) % U == 0
