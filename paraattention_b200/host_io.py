@@ -25,20 +25,30 @@ _SM_COUNT = 148
 
 
 def _default_groups(heads: int, rows: int, batch: int, multiple_of: int, shard: int) -> int:
-    """As many groups (at most 12) as keep every launch large enough, with heads per group a
-    multiple of ``multiple_of``. A CTA covers 256 query rows of one head. On one GPU launches of
-    neighbouring groups overlap (two compute streams), so 1.5 waves of CTAs per launch are
-    enough; context-parallel calls run one after the other and want three waves."""
-    min_ctas = (3 * _SM_COUNT) // 2 if multiple_of * shard == 1 else 3 * _SM_COUNT
+    """How many groups of heads a call is split into; heads per group stay a multiple of
+    ``multiple_of`` (the Ulysses size). A CTA covers 256 query rows of one head.
+
+    One GPU: launches of neighbouring groups overlap (two compute streams), so up to 12 groups
+    as long as a launch still has 1.5 waves of CTAs. Context parallel: the calls of one rank run
+    one after the other and each costs whole rounds of the 148 SMs, so at most 4 groups, and only
+    if splitting adds no more than a tenth to the number of rounds (24 heads on 8 ranks: three
+    calls of 128 CTAs are exactly the three rounds of one call of 384)."""
+    pairs = (rows + 255) // 256
+
+    def ctas(g):
+        return batch * (heads // g // multiple_of) * shard * pairs
+
+    single_gpu = multiple_of * shard == 1
     best = 1
-    for g in range(1, heads + 1):
-        if heads % g:
+    rounds_1 = -(-ctas(1) // _SM_COUNT)
+    for g in range(2, (12 if single_gpu else 4) + 1):
+        if heads % g or (heads // g) % multiple_of:
             continue
-        hg = heads // g
-        if hg % multiple_of:
-            continue
-        ctas = batch * (hg // multiple_of) * shard * ((rows + 255) // 256)
-        if ctas >= min_ctas and g <= 12:
+        if single_gpu:
+            ok = ctas(g) >= (3 * _SM_COUNT) // 2
+        else:
+            ok = g * -(-ctas(g) // _SM_COUNT) <= 1.1 * rounds_1
+        if ok:
             best = g
     return best
 

@@ -295,8 +295,10 @@ def test_host_pipeline_group_choice():
     from paraattention_b200.host_io import _default_groups
 
     assert _default_groups(24, 32760, 1, 1, 1) == 12     # one GPU: launches overlap, 1.5 waves are enough
-    assert _default_groups(24, 16380, 1, 2, 2) == 3      # two ranks: groups of 8 heads, three waves each
-    assert _default_groups(24, 4095, 1, 8, 8) == 1       # eight ranks: three heads per rank, nothing to split
+    assert _default_groups(24, 16380, 1, 2, 2) == 4      # two ranks: 4 x 3 rounds against 11 unsplit
+    assert _default_groups(24, 8190, 1, 4, 4) == 3       # four ranks: 3 x 2 rounds = the 6 unsplit
+    assert _default_groups(24, 4095, 1, 8, 8) == 3       # eight ranks: 3 x 128 CTAs = the three rounds of 384
+    assert _default_groups(24, 576, 1, 8, 8) == 1        # small problem on eight ranks: one call
     assert _default_groups(24, 4608, 1, 1, 1) == 1       # small problem: one launch
     for heads, U in ((24, 2), (40, 8), (6, 3)):
         g = _default_groups(heads, 20000, 1, U, U)
