@@ -27,60 +27,59 @@ _DTYPES = {torch.bfloat16: L.PA_BF16, torch.float16: L.PA_F16}
 
 @dataclasses.dataclass
 class CacheContext:
+    """State of one cached denoising run. The constructor arguments are the reference's
+    (utils.py:12-36); ``apply_cache_on_pipe(**kwargs)`` forwards to them."""
+
     residual_diff_threshold: Union[torch.Tensor, float] = 0.0
     alter_residual_diff_threshold: Optional[Union[torch.Tensor, float]] = None
-
     downsample_factor: int = 1
-
     enable_alter_cache: bool = False
     num_inference_steps: int = -1
     warmup_steps: int = 0
-
     enable_taylorseer: bool = False
     taylorseer_kwargs: Dict[str, Any] = dataclasses.field(default_factory=dict)
-
     slg_layers: Optional[List[int]] = None
     slg_start: float = 0.0
     slg_end: float = 0.1
-
     buffers: Dict[str, Any] = dataclasses.field(default_factory=dict)
     incremental_name_counters: DefaultDict[str, int] = dataclasses.field(default_factory=lambda: defaultdict(int))
-
     executed_steps: int = 0
     is_alter_cache: bool = True
-
     taylorseer: Optional[TaylorSeer] = None
     alter_taylorseer: Optional[TaylorSeer] = None
 
     def __post_init__(self):
-        if self.enable_taylorseer:
-            self.taylorseer = TaylorSeer(**self.taylorseer_kwargs)
-            if self.enable_alter_cache:
-                self.alter_taylorseer = TaylorSeer(**self.taylorseer_kwargs)
+        if not self.enable_taylorseer:
+            return
+        # one extrapolator per cache: the alternate cache (second forward of a step) has its own
+        self.taylorseer = TaylorSeer(**self.taylorseer_kwargs)
+        self.alter_taylorseer = TaylorSeer(**self.taylorseer_kwargs) if self.enable_alter_cache else None
 
+    # -- which of the two caches is current --------------------------------------------------
+    @property
+    def _on_alter(self) -> bool:
+        return self.enable_alter_cache and self.is_alter_cache
+
+    def _name(self, name: str) -> str:
+        return name + "_alter" if self._on_alter else name
+
+    def get_taylorseer(self):
+        return self.alter_taylorseer if self._on_alter else self.taylorseer
+
+    def get_residual_diff_threshold(self):
+        use_alter = self._on_alter and self.alter_residual_diff_threshold is not None
+        threshold = self.alter_residual_diff_threshold if use_alter else self.residual_diff_threshold
+        return threshold.item() if isinstance(threshold, torch.Tensor) else threshold
+
+    # -- named buffers --------------------------------------------------------------------------
     def get_incremental_name(self, name=None):
-        if name is None:
-            name = "default"
-        idx = self.incremental_name_counters[name]
-        self.incremental_name_counters[name] += 1
-        return f"{name}_{idx}"
+        key = "default" if name is None else name
+        index = self.incremental_name_counters[key]
+        self.incremental_name_counters[key] = index + 1
+        return f"{key}_{index}"
 
     def reset_incremental_names(self):
         self.incremental_name_counters.clear()
-
-    def get_residual_diff_threshold(self):
-        if self.enable_alter_cache and self.is_alter_cache and self.alter_residual_diff_threshold is not None:
-            residual_diff_threshold = self.alter_residual_diff_threshold
-        else:
-            residual_diff_threshold = self.residual_diff_threshold
-        if isinstance(residual_diff_threshold, torch.Tensor):
-            residual_diff_threshold = residual_diff_threshold.item()
-        return residual_diff_threshold
-
-    def _name(self, name):
-        if self.enable_alter_cache and self.is_alter_cache:
-            return f"{name}_alter"
-        return name
 
     def get_buffer(self, name):
         return self.buffers.get(self._name(name))
@@ -94,37 +93,17 @@ class CacheContext:
     def clear_buffers(self):
         self.buffers.clear()
 
+    # -- steps ------------------------------------------------------------------------------------
     def mark_step_begin(self):
-        if not self.enable_alter_cache:
-            self.executed_steps += 1
-        else:
+        """Called once per transformer forward. With the alternate cache the two forwards of a
+        step take turns (the flag starts True, so the first forward lands on the main cache)
+        and only the main one counts a step (utils.py:83-92)."""
+        if self.enable_alter_cache:
             self.is_alter_cache = not self.is_alter_cache
-            if not self.is_alter_cache:
-                self.executed_steps += 1
+        if not self._on_alter:
+            self.executed_steps += 1
         if self.enable_taylorseer:
             self.get_taylorseer().mark_step_begin()
-
-    def get_taylorseer(self):
-        if self.enable_alter_cache and self.is_alter_cache:
-            return self.alter_taylorseer
-        return self.taylorseer
-
-    def is_slg_enabled(self):
-        return self.slg_layers is not None
-
-    def slg_should_skip_block(self, block_idx):
-        if not self.enable_alter_cache or not self.is_alter_cache:
-            return False
-        if self.slg_layers is None:
-            return False
-        if self.slg_start <= 0.0 and self.slg_end >= 1.0:
-            return False
-        num_inference_steps = self.num_inference_steps
-        assert num_inference_steps >= 0, "num_inference_steps must be non-negative"
-        return (
-            block_idx in self.slg_layers
-            and num_inference_steps * self.slg_start <= self.get_current_step() < num_inference_steps * self.slg_end
-        )
 
     def get_current_step(self):
         return self.executed_steps - 1
@@ -132,40 +111,57 @@ class CacheContext:
     def is_in_warmup(self):
         return self.get_current_step() < self.warmup_steps
 
+    # -- skip-layer guidance ----------------------------------------------------------------------
+    def is_slg_enabled(self):
+        return self.slg_layers is not None
 
-_current_cache_context = None
+    def slg_should_skip_block(self, block_idx):
+        """Blocks listed in ``slg_layers`` are left out on the alternate forward while the step is
+        inside [slg_start, slg_end) of the schedule (utils.py:102-116)."""
+        if not self._on_alter or self.slg_layers is None:
+            return False
+        if self.slg_start <= 0.0 and self.slg_end >= 1.0:
+            return False
+        total = self.num_inference_steps
+        assert total >= 0, "num_inference_steps must be non-negative"
+        in_window = total * self.slg_start <= self.get_current_step() < total * self.slg_end
+        return in_window and block_idx in self.slg_layers
 
 
-def create_cache_context(*args, **kwargs):
+# The context in force; `cache_context(...)` swaps it for the duration of a pipeline call.
+_current_cache_context: Optional[CacheContext] = None
+
+
+def create_cache_context(*args, **kwargs) -> CacheContext:
     return CacheContext(*args, **kwargs)
 
 
-def get_current_cache_context():
+def get_current_cache_context() -> Optional[CacheContext]:
     return _current_cache_context
 
 
-def set_current_cache_context(cache_context=None):
+def set_current_cache_context(cache_context=None) -> None:
     global _current_cache_context
     _current_cache_context = cache_context
 
 
 @contextlib.contextmanager
 def cache_context(cache_context):
-    global _current_cache_context
-    old_cache_context = _current_cache_context
-    _current_cache_context = cache_context
+    previous = get_current_cache_context()
+    set_current_cache_context(cache_context)
     try:
         yield
     finally:
-        _current_cache_context = old_cache_context
+        set_current_cache_context(previous)
 
 
 def _ctx() -> CacheContext:
-    cache_context = get_current_cache_context()
-    assert cache_context is not None, "cache_context must be set before"
-    return cache_context
+    ctx = get_current_cache_context()
+    assert ctx is not None, "cache_context must be set before"
+    return ctx
 
 
+# Module-level accessors of the reference (utils.py:123-217); each acts on the context in force.
 def get_residual_diff_threshold():
     return _ctx().get_residual_diff_threshold()
 
@@ -315,32 +311,30 @@ def apply_prev_hidden_states_residual(hidden_states, encoder_hidden_states=None)
     return hidden_states, encoder_hidden_states
 
 
+def _every_nth_channel(residual: torch.Tensor, contiguous: bool = False) -> torch.Tensor:
+    """The view of a first-block residual the decision looks at: every ``downsample_factor``-th channel."""
+    factor = get_downsample_factor()
+    if factor <= 1:
+        return residual
+    view = residual[..., ::factor]
+    return view.contiguous() if contiguous else view
+
+
 def get_can_use_cache(first_hidden_states_residual, parallelized=False):
-    """Reference-shaped entry (utils.py:269-286) for callers that already hold the residual."""
-    if is_in_warmup():
-        return False
+    """Reference-shaped entry (utils.py:269-286) for callers that already hold the residual:
+    no reuse during warm-up, with a threshold of zero, or before a first residual exists."""
     threshold = get_residual_diff_threshold()
-    if threshold <= 0.0:
+    if is_in_warmup() or threshold <= 0.0:
         return False
-    downsample_factor = get_downsample_factor()
-    if downsample_factor > 1:
-        first_hidden_states_residual = first_hidden_states_residual[..., ::downsample_factor]
-    prev_first_hidden_states_residual = get_first_hidden_states_residual()
-    can_use_cache = prev_first_hidden_states_residual is not None and are_two_tensors_similar(
-        prev_first_hidden_states_residual,
-        first_hidden_states_residual,
-        threshold=threshold,
-        parallelized=parallelized,
-    )
-    return can_use_cache
+    previous = get_first_hidden_states_residual()
+    if previous is None:
+        return False
+    return are_two_tensors_similar(previous, _every_nth_channel(first_hidden_states_residual), threshold=threshold,
+                                   parallelized=parallelized)
 
 
 def set_first_hidden_states_residual(first_hidden_states_residual):
-    downsample_factor = get_downsample_factor()
-    if downsample_factor > 1:
-        first_hidden_states_residual = first_hidden_states_residual[..., ::downsample_factor]
-        first_hidden_states_residual = first_hidden_states_residual.contiguous()
-    set_buffer("first_hidden_states_residual", first_hidden_states_residual)
+    set_buffer("first_hidden_states_residual", _every_nth_channel(first_hidden_states_residual, contiguous=True))
 
 
 def get_first_hidden_states_residual():
@@ -348,10 +342,11 @@ def get_first_hidden_states_residual():
 
 
 def set_hidden_states_residual(hidden_states_residual):
+    """Keep the residual of the skipped blocks: as a buffer, or as a new sample of the extrapolator."""
     if is_taylorseer_enabled():
         get_taylorseer().update(hidden_states_residual)
-    else:
-        set_buffer("hidden_states_residual", hidden_states_residual)
+        return
+    set_buffer("hidden_states_residual", hidden_states_residual)
 
 
 def get_hidden_states_residual():
@@ -361,9 +356,9 @@ def get_hidden_states_residual():
 
 
 def set_encoder_hidden_states_residual(encoder_hidden_states_residual):
-    if is_taylorseer_enabled():
-        return
-    set_buffer("encoder_hidden_states_residual", encoder_hidden_states_residual)
+    # under TaylorSeer only the hidden states are extrapolated; the encoder states pass through
+    if not is_taylorseer_enabled():
+        set_buffer("encoder_hidden_states_residual", encoder_hidden_states_residual)
 
 
 def get_encoder_hidden_states_residual():
@@ -390,95 +385,91 @@ def first_block_decision(hidden_states, original_hidden_states, parallelized=Fal
 
 
 class CachedTransformerBlocks(torch.nn.Module):
-    def __init__(
-        self,
-        transformer_blocks,
-        single_transformer_blocks=None,
-        *,
-        transformer=None,
-        return_hidden_states_first=True,
-        return_hidden_states_only=False,
-    ):
-        super().__init__()
+    """Stands in for a transformer's block list (src/para_attn/first_block_cache/utils.py:333-451):
+    runs the first block, decides from its residual whether the rest can be skipped, and either
+    applies the cached residual or runs the remaining blocks and caches theirs.
 
+    Blocks take ``(hidden_states, encoder_hidden_states, ...)`` and return a tensor or a pair - in
+    the order given by ``return_hidden_states_first`` - which is also what this module returns
+    (``return_hidden_states_only`` drops the encoder states). ``single_transformer_blocks`` work on
+    the concatenation [encoder states, hidden states] along the sequence."""
+
+    def __init__(self, transformer_blocks, single_transformer_blocks=None, *, transformer=None,
+                 return_hidden_states_first=True, return_hidden_states_only=False):
+        super().__init__()
         self.transformer = transformer
         self.transformer_blocks = transformer_blocks
         self.single_transformer_blocks = single_transformer_blocks
         self.return_hidden_states_first = return_hidden_states_first
         self.return_hidden_states_only = return_hidden_states_only
 
-    def _unpack(self, hidden_states, encoder_hidden_states):
-        if not isinstance(hidden_states, torch.Tensor):
-            hidden_states, encoder_hidden_states = hidden_states
-            if not self.return_hidden_states_first:
-                hidden_states, encoder_hidden_states = encoder_hidden_states, hidden_states
-        return hidden_states, encoder_hidden_states
+    # -- block calling conventions ------------------------------------------------------------
+    def _unpack(self, result, encoder_hidden_states):
+        """(hidden, encoder) from what a block returned; a bare tensor leaves the encoder states as they were."""
+        if isinstance(result, torch.Tensor):
+            return result, encoder_hidden_states
+        first, second = result
+        return (first, second) if self.return_hidden_states_first else (second, first)
 
+    def _pack(self, hidden_states, encoder_hidden_states):
+        if self.return_hidden_states_only:
+            return hidden_states
+        if self.return_hidden_states_first:
+            return hidden_states, encoder_hidden_states
+        return encoder_hidden_states, hidden_states
+
+    def _is_parallelized(self) -> bool:
+        return self.transformer is not None and getattr(self.transformer, "_is_parallelized", False)
+
+    # -- one transformer forward ------------------------------------------------------------------
     def forward(self, hidden_states, encoder_hidden_states, *args, **kwargs):
-        original_hidden_states = hidden_states
-        first_transformer_block = self.transformer_blocks[0]
-        hidden_states = first_transformer_block(hidden_states, encoder_hidden_states, *args, **kwargs)
-        hidden_states, encoder_hidden_states = self._unpack(hidden_states, encoder_hidden_states)
+        block_input = hidden_states
+        hidden_states, encoder_hidden_states = self._unpack(
+            self.transformer_blocks[0](hidden_states, encoder_hidden_states, *args, **kwargs), encoder_hidden_states)
 
         mark_step_begin()
-        can_use_cache = first_block_decision(
-            hidden_states,
-            original_hidden_states,
-            parallelized=self.transformer is not None and getattr(self.transformer, "_is_parallelized", False),
-        )
-        del original_hidden_states
+        reuse = first_block_decision(hidden_states, block_input, parallelized=self._is_parallelized())
+        del block_input
 
-        if can_use_cache:
-            hidden_states, encoder_hidden_states = apply_prev_hidden_states_residual(
-                hidden_states, encoder_hidden_states
-            )
+        if reuse:
+            hidden_states, encoder_hidden_states = apply_prev_hidden_states_residual(hidden_states,
+                                                                                     encoder_hidden_states)
         else:
-            (
-                hidden_states,
-                encoder_hidden_states,
-                hidden_states_residual,
-                encoder_hidden_states_residual,
-            ) = self.call_remaining_transformer_blocks(hidden_states, encoder_hidden_states, *args, **kwargs)
-            set_hidden_states_residual(hidden_states_residual)
-            set_encoder_hidden_states_residual(encoder_hidden_states_residual)
-
-        return (
-            hidden_states
-            if self.return_hidden_states_only
-            else (
-                (hidden_states, encoder_hidden_states)
-                if self.return_hidden_states_first
-                else (encoder_hidden_states, hidden_states)
-            )
-        )
+            hidden_states, encoder_hidden_states, residual, encoder_residual = \
+                self.call_remaining_transformer_blocks(hidden_states, encoder_hidden_states, *args, **kwargs)
+            set_hidden_states_residual(residual)
+            set_encoder_hidden_states_residual(encoder_residual)
+        return self._pack(hidden_states, encoder_hidden_states)
 
     def call_remaining_transformer_blocks(self, hidden_states, encoder_hidden_states, *args, **kwargs):
-        original_hidden_states = hidden_states
-        original_encoder_hidden_states = encoder_hidden_states
-        slg = is_slg_enabled()
-        for i, block in enumerate(self.transformer_blocks[1:]):
-            if slg and slg_should_skip_block(i + 1):
+        """Blocks 1.. of the joint list, then the single-stream list; returns the new states and
+        their residuals against the states this method was entered with (utils.py:402-451)."""
+        entry_hidden, entry_encoder = hidden_states, encoder_hidden_states
+        skip = slg_should_skip_block if is_slg_enabled() else (lambda index: False)
+        n_joint = len(self.transformer_blocks)
+
+        for index in range(1, n_joint):
+            if skip(index):
                 continue
-            hidden_states = block(hidden_states, encoder_hidden_states, *args, **kwargs)
-            hidden_states, encoder_hidden_states = self._unpack(hidden_states, encoder_hidden_states)
+            out = self.transformer_blocks[index](hidden_states, encoder_hidden_states, *args, **kwargs)
+            hidden_states, encoder_hidden_states = self._unpack(out, encoder_hidden_states)
+
         if self.single_transformer_blocks is not None:
-            hidden_states = torch.cat([encoder_hidden_states, hidden_states], dim=1)
-            for i, block in enumerate(self.single_transformer_blocks):
-                if slg and slg_should_skip_block(len(self.transformer_blocks) + i):
-                    continue
-                hidden_states = block(hidden_states, *args, **kwargs)
-            encoder_hidden_states, hidden_states = hidden_states.split(
-                [encoder_hidden_states.shape[1], hidden_states.shape[1] - encoder_hidden_states.shape[1]], dim=1
-            )
+            n_text = encoder_hidden_states.shape[1]
+            joint = torch.cat([encoder_hidden_states, hidden_states], dim=1)
+            for offset, block in enumerate(self.single_transformer_blocks):
+                if not skip(n_joint + offset):
+                    joint = block(joint, *args, **kwargs)
+            encoder_hidden_states, hidden_states = joint.split([n_text, joint.shape[1] - n_text], dim=1)
 
-        hidden_states = hidden_states.reshape(-1).contiguous().reshape(original_hidden_states.shape)
-        hidden_states_residual = _axpy(hidden_states, original_hidden_states.contiguous(), sub=True)
-        encoder_hidden_states_residual = None
+        def settle(states, entry):
+            # a dense copy in the entry tensor's shape (the split above hands out strided views),
+            # and the residual against the entry states in the same launch-sized pass
+            states = states.reshape(-1).contiguous().reshape(entry.shape)
+            return states, _axpy(states, entry.contiguous(), sub=True)
+
+        hidden_states, residual = settle(hidden_states, entry_hidden)
+        encoder_residual = None
         if encoder_hidden_states is not None:
-            encoder_hidden_states = (
-                encoder_hidden_states.reshape(-1).contiguous().reshape(original_encoder_hidden_states.shape)
-            )
-            encoder_hidden_states_residual = _axpy(
-                encoder_hidden_states, original_encoder_hidden_states.contiguous(), sub=True)
-
-        return hidden_states, encoder_hidden_states, hidden_states_residual, encoder_hidden_states_residual
+            encoder_hidden_states, encoder_residual = settle(encoder_hidden_states, entry_encoder)
+        return hidden_states, encoder_hidden_states, residual, encoder_residual

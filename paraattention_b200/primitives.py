@@ -5,95 +5,95 @@ it is done by the peer-store kernels of libpa_b200 (see ``_cp_engine``). What re
 are the group accessors, the shard/unshard helpers called once per transformer forward, and
 synchronous NCCL/gloo collectives for the small control-plane messages (seed agreement,
 the two cache scalars, the exit all-gather).
+
+Every ``group`` argument accepts ``None`` (the default group), a ``ProcessGroup`` or a
+one-dimensional ``DeviceMesh``.
 """
-from typing import List, Optional, Tuple, Union
+from typing import Optional, Sequence, Union
 
 import torch
 import torch.distributed as dist
-import torch.distributed._functional_collectives as ft_c
-import torch.distributed.distributed_c10d as c10d
+import torch.distributed._functional_collectives as funcol
+from torch.distributed.distributed_c10d import _get_default_group
 
 
-def get_default_group():
-    return c10d._get_default_group()
+# ------------------------------------------------------------------------------------------
+# groups
+# ------------------------------------------------------------------------------------------
+def get_default_group() -> dist.ProcessGroup:
+    return _get_default_group()
 
 
-def get_group(group=None):
-    if group is None:
-        group = c10d._get_default_group()
+def get_group(group=None) -> dist.ProcessGroup:
     if isinstance(group, dist.ProcessGroup):
         return group
-    return group.get_group()
+    return _get_default_group() if group is None else group.get_group()  # DeviceMesh -> its group
 
 
-def get_world_size(group=None):
+def get_world_size(group=None) -> int:
     return dist.get_world_size(get_group(group))
 
 
-def get_rank(group=None):
+def get_rank(group=None) -> int:
     return dist.get_rank(get_group(group))
 
 
-def _maybe_wait(tensor: torch.Tensor) -> torch.Tensor:
-    if isinstance(tensor, ft_c.AsyncCollectiveTensor):
-        return tensor.wait()
-    return tensor
+# ------------------------------------------------------------------------------------------
+# collectives that return finished tensors (functional collectives hand out lazy ones)
+# ------------------------------------------------------------------------------------------
+def _finished(t: torch.Tensor) -> torch.Tensor:
+    return t.wait() if isinstance(t, funcol.AsyncCollectiveTensor) else t
 
 
 def all_gather_tensor_sync(x, *args, group=None, **kwargs):
-    group = get_group(group)
-    x_shape = list(x.shape)
-    x = x.flatten()
-    x_numel = x.numel()
-    x = _maybe_wait(ft_c.all_gather_tensor(x, *args, group=group, **kwargs))
-    x_shape[0] *= x.numel() // x_numel
-    return x.reshape(x_shape)
+    """All-gather along dim 0; works on the flattened tensor so that any trailing shape is kept."""
+    lead, rest = x.shape[0], tuple(x.shape[1:])
+    flat = x.flatten()
+    gathered = _finished(funcol.all_gather_tensor(flat, *args, group=get_group(group), **kwargs))
+    copies = gathered.numel() // max(flat.numel(), 1)
+    return gathered.reshape((lead * copies,) + rest)
 
 
 def all_to_all_single_sync(x, *args, **kwargs):
-    x_shape = x.shape
-    x = _maybe_wait(ft_c.all_to_all_single(x.flatten(), *args, **kwargs))
-    return x.reshape(x_shape)
+    """Equal-split all-to-all along the flattened tensor, reshaped back (used by callers that
+    keep the reference's exchange; the fused attention path does not call it)."""
+    return _finished(funcol.all_to_all_single(x.flatten(), *args, **kwargs)).reshape(x.shape)
 
 
 def all_reduce_sync(x, *args, group=None, **kwargs):
-    group = get_group(group)
-    return _maybe_wait(ft_c.all_reduce(x, *args, group=group, **kwargs))
+    return _finished(funcol.all_reduce(x, *args, group=get_group(group), **kwargs))
 
 
-def get_buffer(
-    shape_or_tensor: Union[Tuple[int], torch.Tensor],
-    *,
-    repeats: int = 1,
-    dim: int = 0,
-    dtype: Optional[torch.dtype] = None,
-    device: Optional[torch.device] = None,
-    group=None,
-) -> torch.Tensor:
-    if repeats is None:
-        repeats = get_world_size(group)
+# ------------------------------------------------------------------------------------------
+# sharding helpers
+# ------------------------------------------------------------------------------------------
+def get_buffer(shape_or_tensor: Union[Sequence[int], torch.Tensor], *, repeats: int = 1, dim: int = 0,
+               dtype: Optional[torch.dtype] = None, device: Optional[torch.device] = None, group=None) -> torch.Tensor:
+    """An uninitialised tensor shaped like ``shape_or_tensor`` with ``dim`` enlarged ``repeats``
+    times (``repeats=None``: once per rank of ``group``) - a receive buffer for gathers."""
     if isinstance(shape_or_tensor, torch.Tensor):
-        shape, dtype, device = shape_or_tensor.shape, shape_or_tensor.dtype, shape_or_tensor.device
+        like = shape_or_tensor
+        shape, dtype, device = list(like.shape), like.dtype, like.device
     else:
-        shape = shape_or_tensor
+        shape = list(shape_or_tensor)
     assert dtype is not None
     assert device is not None
-    shape = list(shape)
-    if repeats > 1:
-        shape[dim] *= repeats
+    factor = get_world_size(group) if repeats is None else repeats
+    if factor > 1:
+        shape[dim] = shape[dim] * factor
     return torch.empty(shape, dtype=dtype, device=device)
 
 
 def get_assigned_chunk(tensor: torch.Tensor, dim: int = 0, idx: Optional[int] = None, group=None) -> torch.Tensor:
-    if idx is None:
-        idx = get_rank(group)
+    """This rank's (or rank ``idx``'s) equal share of ``tensor`` along ``dim``; uneven splits are refused."""
     world_size = get_world_size(group)
     total_size = tensor.shape[dim]
     assert total_size % world_size == 0, f"tensor.shape[{dim}]={total_size} is not divisible by world_size={world_size}"
-    return tensor.chunk(world_size, dim=dim)[idx]
+    which = get_rank(group) if idx is None else idx
+    return tensor.chunk(world_size, dim=dim)[which]
 
 
 def get_complete_tensor(tensor: torch.Tensor, *, dim: int = 0, group=None) -> torch.Tensor:
-    tensor = tensor.transpose(0, dim).contiguous()
-    output_tensor = all_gather_tensor_sync(tensor, gather_dim=0, group=group)
-    return output_tensor.transpose(0, dim)
+    """Inverse of ``get_assigned_chunk``: the shards of all ranks concatenated along ``dim``."""
+    moved = tensor.transpose(0, dim).contiguous()  # the gather concatenates along dim 0
+    return all_gather_tensor_sync(moved, gather_dim=0, group=group).transpose(0, dim)

@@ -303,3 +303,53 @@ def test_host_pipeline_group_choice():
     for heads, U in ((24, 2), (40, 8), (6, 3)):
         g = _default_groups(heads, 20000, 1, U, U)
         assert heads % g == 0 and (heads // g) % U == 0
+
+
+def _adapter_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from paraattention_b200.context_parallel.diffusers_adapters import parallelize_transformer
+    from paraattention_b200.shape_models import FluxShapedPipeline, FluxShapedTransformer2DModel
+    from paraattention_b200.shape_models_hunyuan import HunyuanVideoShapedTransformer3DModel
+    from paraattention_b200.shape_models_video import WanShapedTransformer3DModel
+
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, 16, 2, 8, 8, generator=g)
+    enc, pooled, t = torch.randn(1, 8, 64, generator=g), torch.randn(1, 32, generator=g), torch.tensor([500.0])
+    errs = {}
+    torch.manual_seed(0)
+    wan = WanShapedTransformer3DModel(dim=256, num_layers=2, ffn_dim=512, text_dim=64)
+    want = wan(x, t, enc).sample
+    errs["wan"] = (parallelize_transformer(wan)(x, t, enc).sample - want).abs().max().item()
+    torch.manual_seed(0)
+    hun = HunyuanVideoShapedTransformer3DModel(dim=256, num_layers=2, num_single_layers=2, text_dim=64,
+                                               pooled_projection_dim=32)
+    mask, guidance = torch.ones(1, 8), torch.tensor([6.0])
+    want = hun(x, t, enc, mask, pooled, guidance=guidance).sample
+    errs["hunyuan"] = (parallelize_transformer(hun)(x, t, enc, mask, pooled, guidance=guidance).sample - want).abs().max().item()
+    torch.manual_seed(0)
+    flux = FluxShapedTransformer2DModel(dim=256, num_layers=2, num_single_layers=2, joint_attention_dim=64)
+    pipe = FluxShapedPipeline(flux, text_tokens=8, latent_hw=(4, 4))
+    want = pipe(num_inference_steps=2, generator=torch.Generator().manual_seed(3))
+    parallelize_transformer(flux)
+    errs["flux"] = (pipe(num_inference_steps=2, generator=torch.Generator().manual_seed(3)) - want).abs().max().item()
+    ret.put(errs)
+    dist.destroy_process_group()
+
+
+def test_adapters_restate_the_forward_exactly_on_one_rank():
+    """With a single rank every shard is the whole tensor, so the adapters' re-stated forwards
+    (patch grid, embeddings, output projection, un-patchify) must reproduce the models' own
+    outputs; runs on CPU in fp32, where attention falls through to PyTorch."""
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    p = ctx.Process(target=_adapter_worker, args=(0, 1, 29656, ret))
+    p.start()
+    errs = ret.get(timeout=300)
+    p.join(timeout=60)
+    for name, e in errs.items():
+        assert e < 1e-5, f"{name}: adapter output differs from the model's by {e:.3e}"
