@@ -142,3 +142,41 @@ def test_taylorseer_bit_exact_against_reference(golden_dir, case, kw):
     for t in range(ys.shape[0]):
         got = seer.step(ys[t])
         assert np.array_equal(got, _f32(g[case][t])), f"{case}: step {t} differs"
+
+
+@pytest.mark.parametrize("U,R", [(2, 1), (1, 2), (2, 2), (4, 2), (1, 8)])
+def test_causal_composition_equals_whole_sequence_causal(U, R):
+    """The oracle's Ulysses-around-causal-ring composition (step 0 causal, earlier ranks in full,
+    later ranks skipped) is plain causal attention over the sequence sharded in flat-rank order."""
+    W = U * R
+    rng = np.random.default_rng(U * 10 + R)
+    H, s, D = 2 * U, 24, 16
+    q, k, v = (rng.standard_normal((1, H, W * s, D)).astype(np.float32) for _ in range(3))
+    qs, ks, vs = (_shards(x, W) for x in (q, k, v))
+    outs = O.unified_attention(qs, ks, vs, ulysses=U, ring=R, is_causal=True)
+    whole, _ = O.sdpa_with_lse(q, k, v, is_causal=True)
+    np.testing.assert_allclose(np.concatenate(outs, axis=-2), whole, rtol=2e-5, atol=2e-6)
+
+
+def test_key_mask_composes_with_chunks():
+    """Masked attention over the whole sequence equals merging per-chunk masked attention: what
+    the chunked kernel relies on when a mask meets ring chunks."""
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((2, 2, 40, 16)).astype(np.float32) for _ in range(3))
+    mask = rng.random((2, 40)) < 0.6
+    mask[1, 20:] = False  # second chunk of batch element 1 is all padding
+    whole, whole_lse = O.sdpa_with_lse(q, k, v, key_mask=mask)
+    out = lse = None
+    for c in range(2):
+        sl = slice(c * 20, (c + 1) * 20)
+        o_c, l_c = O.sdpa_with_lse(q, k[:, :, sl], v[:, :, sl], key_mask=mask[:, sl])
+        if out is None:
+            out, lse = o_c, l_c
+            continue
+        # a chunk without any visible key carries LSE = -inf and must not disturb the merge
+        dead = np.isneginf(l_c)
+        with np.errstate(over="ignore"):  # the stand-in for -inf overflows exp(); those rows are discarded
+            m_out, m_lse = O.merge_out_lse(out, lse, o_c, np.where(dead, -1e30, l_c))
+        out, lse = np.where(dead[..., None], out, m_out), np.where(dead, lse, m_lse)
+    np.testing.assert_allclose(out, whole, rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(lse, whole_lse, rtol=2e-5, atol=2e-6)
