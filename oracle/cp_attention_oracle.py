@@ -1,4 +1,5 @@
-"""CPU oracle for the context-parallel attention path and the First-Block-Cache decision.
+"""CPU oracle for the context-parallel attention path, key-padding masks, the First-Block-Cache
+decision and its TaylorSeer extrapolation.
 
 TEST INFRASTRUCTURE ONLY. This module is a numpy restatement of the arithmetic the
 ParaAttention reference performs for its ring / Ulysses / unified attention and for the
@@ -6,9 +7,10 @@ cache decision. It exists to check the CUDA library and must never be imported b
 product package: only the tests, ``__graft_entry__.smoke()`` and the CPU-baseline legs of
 ``bench.py`` use it.
 
-Pinning: ``tests/golden/make_golden.py`` runs the reference itself (CPU, gloo, fp32) and
-stores its inputs and outputs; ``tests/test_oracle.py`` checks every function below
-against those fixtures.
+Pinning: ``tests/golden/make_golden.py`` runs the reference itself (CPU, gloo, fp32 attention;
+bf16 cache and TaylorSeer tensors) and stores its inputs and outputs; ``tests/test_oracle.py``
+checks every function below against those fixtures (attention to 2e-6, cache decisions
+identical, TaylorSeer outputs bit for bit).
 
 Citations are ``file:line`` in the ParaAttention source tree; ``torch:`` marks
 torch/distributed/tensor/experimental/_context_parallel/_attention.py of PyTorch 2.11,
