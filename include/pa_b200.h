@@ -164,18 +164,6 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);
 int pa_pack_key_mask(const uint8_t* mask, int64_t batch_stride, int32_t batch, int32_t n_chunks, int32_t rows,
                      uint64_t* out, void* stream);
 
-/* Test hook: pa_attn_fwd that also dumps the raw q k^T tiles of the first CTA to dbg_s
- * ([2][kv_tiles][128][128] floats, may be NULL) and lets the caller choose the shared-memory
- * descriptor strides of V (v_lbo, v_sbo; bytes) and whether P V is issued as two N=64 MMAs.
- * No counterpart in the reference. */
-int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo, int pv_split, void* stream);
-
-/* Test hook: pa_attn_fwd whose first CTA records clock64() stamps of its pipeline phases for
- * the first `steps` key/value tiles into stamps[3][steps][8] (roles: softmax of query tile 0,
- * softmax of query tile 1, MMA issuer). Used to read the kernel's timeline without a
- * profiler. No counterpart in the reference. */
-int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps, void* stream);
-
 /* ------------------------------------------------------------------------------------------
  * Exchange. Replaces the NCCL all_to_all_single calls of _sdpa_input_all_to_all /
  * _sdpa_output_all_to_all (src/para_attn/para_attn_interface.py:52-87, through

@@ -106,8 +106,6 @@ def load() -> C.CDLL:
     lib.pa_version.restype = C.c_int
     lib.pa_attn_fwd.restype = C.c_int
     lib.pa_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
-    lib.pa_dbg_attn_fwd.restype = C.c_int
-    lib.pa_dbg_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     lib.pa_cp_attn_fwd.restype = C.c_int
     lib.pa_cp_attn_fwd.argtypes = [C.POINTER(CpAttnArgs), C.c_void_p]
     lib.pa_taylor_update.restype = C.c_int

@@ -1,20 +1,30 @@
 // Flash-attention forward for B200 (sm_100a): tcgen05 MMA with TMEM accumulators, TMA loads.
 //
 // One CTA owns two query tiles of 128 rows (same batch/head/chunk) and walks every key/value
-// tile of 128 rows. Warp roles (20 warps):
-//   warps 0-15  softmax. Warp w serves TMEM lane quarter w%4 (32 query rows) of query tile
-//               (w/4)%2 and key-column half w/8: two threads share a query row, each owns
-//               64 of the tile's 128 key columns (and, in the epilogue, half of O's columns).
-//   warp  16    MMA issuer (one thread): S_t = Q_t K_j^T into TMEM, O_t += P_t V_j from TMEM
-//   warp  17    TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
-//   warps 18-19 idle; they complete the control warpgroup that gives registers away
+// tile of 128 rows. Warp roles (10 warps):
+//   warps 0-7   softmax: one thread per query row. Warp w serves TMEM lane quarter w%4 (32 query
+//               rows) of query tile w/4 - all 128 key columns of a tile and, in the epilogue,
+//               the whole output row.
+//   warp  8     MMA issuer (the warp in lockstep, one elected lane issues): S_t = Q_t K_j^T into
+//               TMEM, O_t += P_t V_j from TMEM
+//   warp  9     TMA producer (one thread): Q once, then K_j / V_j through a 2-stage ring
 // TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512) for
 // head_dim 128 (O0 [256,320) O1 [320,384) for head_dim 64);
-// P_t (bf16/f16) overwrites S_t in place - each thread packs its 64 probabilities into the
-// first 32 of its own 64 logit columns - and is the TMEM A operand of P V.
-// While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs; the
-// two column halves of P are handed over separately, so P V starts on the first half while the
-// second is still being exponentiated.
+// P_t (bf16/f16) overwrites S_t in place: the probabilities of key columns [32c, 32c+32) are
+// packed into S columns [16c, 16c+16), which are consumed by then, and P is the TMEM A operand
+// of P V. While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs.
+//
+// What bounds this kernel is each tile's chain softmax -> P V -> next Q K^T -> softmax, so the
+// softmax is arranged to keep that chain short:
+//  * ONE pass over the logits, 32 columns at a time (the next 32 in flight): a chunk is
+//    exponentiated against the row reference - a maximum seen earlier - while its own maximum
+//    is found on the side. If no row of the warp outgrew its reference by more than 2^8 (the
+//    headroom that a lazily rescaled O allows anyway), the chunk's probabilities are stored
+//    and handed to the tensor core at once, so P V of the first key columns runs while the
+//    later ones are still being exponentiated. If some row did (the first chunk of a row
+//    always does), the warp waits for the P V issued so far, moves the reference up, rescales
+//    its rows of O and redoes that chunk from the logits it still holds in registers.
+//  * no exchange between threads: a row's maximum, sum and O belong to one thread.
 //
 // In context-parallel runs the same launch also performs the exchange (see the fused push
 // below): one kernel per attention call and rank, no collective library call on the path.
@@ -36,6 +46,10 @@
 #include "pa_ptx.cuh"
 #include "cp_exchange_sm100.cuh"
 
+#ifndef PA_TIMELINE
+#define PA_TIMELINE 0
+#endif
+
 namespace pa {
 
 // head_dim is a template parameter of the kernel (kD = 64 or 128). Shared-memory slots keep
@@ -45,24 +59,24 @@ constexpr int kTileN = 128;
 constexpr int kHalfBytes = 128 * 128;       // 128 rows x 64 elements x 2 B (one swizzle atom wide)
 constexpr int kTileBytes = 2 * kHalfBytes;  // 128 x 128 x 2 B
 constexpr int kStages = 2;
-constexpr int kSoftmaxWarps = 16;
-constexpr int kMmaWarp = 16;
-constexpr int kTmaWarp = 17;
-constexpr int kAttnThreads = 640;  // 4 softmax warpgroups + 1 control warpgroup
+constexpr int kSoftmaxWarps = 8;
+constexpr int kMmaWarp = 8;
+constexpr int kTmaWarp = 9;
+constexpr int kAttnThreads = 384;  // 2 softmax warpgroups + 1 control warpgroup
+constexpr int kRegsLaunch = 168;   // 65536 / 384, rounded down to a multiple of 8
 #ifndef PA_REGS_SOFTMAX
-#define PA_REGS_SOFTMAX 104
+#define PA_REGS_SOFTMAX 168
 #endif
 #ifndef PA_REGS_CONTROL
-#define PA_REGS_CONTROL 64
+#define PA_REGS_CONTROL 168
 #endif
-constexpr int kRegsLaunch = 96;  // 65536 / 640 rounded down to a multiple of 8
 constexpr int kRegsSoftmax = PA_REGS_SOFTMAX;
 constexpr int kRegsControl = PA_REGS_CONTROL;
-// Each scheduler partition holds one warp of each of the five warpgroups, so what its four
-// softmax warps gain must be covered by what its control warp gives up - otherwise
-// setmaxnreg.inc would wait forever.
-static_assert(4 * kRegsSoftmax + kRegsControl <= 5 * kRegsLaunch, "setmaxnreg budget exceeds the launch allocation");
+static_assert(2 * kRegsSoftmax + kRegsControl <= 3 * kRegsLaunch, "setmaxnreg budget exceeds the launch allocation");
 static_assert(kRegsSoftmax % 8 == 0 && kRegsControl % 8 == 0, "setmaxnreg counts are multiples of 8");
+constexpr int kPieces = 4;         // P is handed to the tensor core in pieces of 32 key columns
+constexpr int kPieceCols = kTileN / kPieces;
+static_assert(kPieceCols == 32, "the softmax loads and hands over 32 columns at a time");
 constexpr int kTmemCols = 512;
 constexpr uint32_t kColS0 = 0, kColO0 = 256;
 // log2-domain growth of the running row maximum that is tolerated before O is rescaled
@@ -72,10 +86,6 @@ constexpr float kRescaleThreshold = 8.0f;
 #define PA_POLY_PAIRS_OF_8 0
 #endif
 constexpr int kPolyPairsOf8 = PA_POLY_PAIRS_OF_8;
-#ifndef PA_POLY_HALF1
-#define PA_POLY_HALF1 0
-#endif
-constexpr bool kPolyHalf1 = PA_POLY_HALF1 != 0;
 
 struct AttnParams {
     int batch, heads;
@@ -103,54 +113,121 @@ struct AttnParams {
     // row i of that chunk may be attended to; strides in 64-bit words
     const unsigned long long* key_bits;
     long long kb_sb, kb_sc;
-    // debug instantiation only
-    float* dbg_s;      // raw S of CTA 0: [tile][kv tile][row][col]
-    int v_lbo, v_sbo;  // B descriptor of V (bytes)
-    int pv_split;      // 1: issue P V as two N=64 MMAs
-    long long* dbg_t;  // clock64 stamps of CTA 0: [role 0..2][step][8]; roles: softmax 0, softmax 1, MMA issuer
+#if PA_TIMELINE
+    long long* dbg_t;  // clock64 stamps of CTA 0: [role 0..4][step][8]; roles: softmax 0, softmax 1, MMA issuer, TMA producer, MMA operand waits
     int dbg_steps;
+#endif
 };
 
-#ifndef PA_TIMELINE
-#define PA_TIMELINE 0  // 1: the stamps are also compiled into the production instantiation (profiling builds)
-#endif
-template <bool kDebug>
+// Profiling builds (-DPA_TIMELINE=1, never the shipped library) let the first CTA record
+// clock64() stamps of its pipeline phases; in every other build the calls compile to nothing.
 __device__ __forceinline__ void dbg_stamp(const AttnParams& p, int role, int step, int slot, bool who) {
-    if (kDebug || PA_TIMELINE) {
-        if (p.dbg_t != nullptr && blockIdx.x == 0 && who && step < p.dbg_steps)
-            p.dbg_t[(static_cast<size_t>(role) * p.dbg_steps + step) * 8 + slot] = clock64();
-    }
+#if PA_TIMELINE
+    if (p.dbg_t != nullptr && blockIdx.x == 0 && who && step < p.dbg_steps)
+        p.dbg_t[(static_cast<size_t>(role) * p.dbg_steps + step) * 8 + slot] = clock64();
+#endif
 }
 
 struct AttnSmemCtl {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages];
     uint64_t v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2], p_full[2][2], o_done[2];
+    uint64_t s_full[2];           // Q K^T of a query tile is in TMEM
+    uint64_t p_full[2][kPieces];  // a piece of P of a query tile is in TMEM (128 arrivals)
+    uint64_t o_done[2][kPieces];  // P V of a piece (and every MMA issued before it) is done
     uint64_t teardown;
     uint32_t tmem_base;
     int abort;
-    float xch[2][2][2][kTileM];  // [step parity][query tile][column half][row]: row max / row sum exchange
 };
 
-constexpr int kAttnCtlBytes = 4608;
+constexpr int kAttnCtlBytes = 512;
 constexpr int kAttnSmemBytes = 1024 /*align slack*/ + 2 * kTileBytes /*Q*/ +
                                kStages * kTileBytes /*K*/ + kStages * kTileBytes /*V*/ + kAttnCtlBytes;
 static_assert(sizeof(AttnSmemCtl) <= kAttnCtlBytes, "control block too large");
 
-// Barrier among the 64 threads (two warps) that share 32 query rows.
-__device__ __forceinline__ void pair_sync(int id) {
-    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+// Softmax of one thread over 32 logits held in registers: p = 2^(s * sl + neg) packed to 16-bit
+// pairs (pk[i] = columns 2i, 2i+1), their fp32 sum, and the largest raw logit. With kMasked, columns whose bit in
+// `live` is clear count as -inf (the unmasked instantiation carries no per-element mask code at
+// all: it is the one that runs on every full tile). kPolyPairsOf8 of every 8 pairs take an
+// FMA-pipe polynomial instead of the special-function unit (off by default).
+template <bool kBF16, bool kMasked>
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&sc)[32], uint32_t live, float sl, float neg,
+                                              uint32_t (&pk)[16], float& sum, float& mx) {
+    const float2 sl2 = make_float2(sl, sl);
+    const float2 neg2 = make_float2(neg, neg);
+    float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    float m[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        float s0 = __uint_as_float(sc[i]), s1 = __uint_as_float(sc[i + 1]);
+        if (kMasked) {
+            if (((live >> i) & 1u) == 0) s0 = -INFINITY;
+            if (((live >> (i + 1)) & 1u) == 0) s1 = -INFINITY;
+        }
+        m[(i >> 1) & 1] = fmax3(m[(i >> 1) & 1], s0, s1);
+        const float2 x = __ffma2_rn(make_float2(s0, s1), sl2, neg2);
+        float2 e;
+        if (((i >> 1) & 7) < kPolyPairsOf8) {
+            e = exp2_poly2(x);
+        } else {
+            e.x = ex2_approx(x.x);
+            e.y = ex2_approx(x.y);
+        }
+        ls[(i >> 1) & 1] = __fadd2_rn(ls[(i >> 1) & 1], e);
+        pk[i >> 1] = kBF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
+    }
+    const float2 t = __fadd2_rn(ls[0], ls[1]);
+    sum = t.x + t.y;
+    mx = fmaxf(m[0], m[1]);
 }
 
-template <bool kBF16, bool kDebug, bool kCausal, int kD>
+// The rare path of a softmax piece, kept out of line so that the loop every tile runs stays
+// small: some row of the calling warp (all 32 lanes call) outgrew its reference `m_ref` with
+// this piece's maximum `mx`. Every row moves its reference up to what it has seen; once the
+// P V handed over so far has completed (`wait_o`: barrier `bo`, phase parity `par`) the warp's
+// rows of O at `tO` are rescaled; the piece is reloaded from `tS_piece`, exponentiated against
+// the new reference and stored to `tP`. Returns the new reference and the new row sum.
+template <bool kBF16, int kD>
+__device__ __noinline__ float2 softmax_piece_regrow(uint32_t tS_piece, uint32_t tP, uint32_t tO, uint32_t live, float sl,
+                                                    float mx, float m_ref, float l_sum, bool wait_o, uint32_t bo,
+                                                    uint32_t par, volatile int* s_abort, int* status,
+                                                    unsigned long long limit_ns) {
+    const float m_new = fmaxf(m_ref, mx);
+    // (a row that has seen no visible key yet keeps m = -inf: scale by 1, not by NaN)
+    const float alpha = (m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl);
+    if (wait_o) {
+        mbar_wait(bo, par, s_abort, status, limit_ns, PA_DEV_TIMEOUT_PIPE);
+        tc_fence_after();
+#pragma unroll
+        for (int b = 0; b < kD / 32; ++b) {
+            uint32_t o[32];
+            tmem_ld32(tO + b * 32, o);
+            tc_wait_ld();
+            tmem_ld_fence(o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + b * 32, o);
+        }
+        // (ordered before the next P V by the caller's wait::st / fence / arrive for this piece)
+    }
+    uint32_t sc[32];
+    tmem_ld32(tS_piece, sc);
+    tc_wait_ld();
+    tmem_ld_fence(sc);
+    uint32_t pk[16];
+    float ls, unused;
+    softmax_chunk<kBF16, true>(sc, live, sl, (m_new == -INFINITY) ? 0.0f : -m_new * sl, pk, ls, unused);
+    tmem_st16(tP, pk);
+    return make_float2(m_new, l_sum * alpha + ls);
+}
+
+template <bool kBF16, bool kCausal, int kD>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ql,
                 const __grid_constant__ CUtensorMap tm_kl, const __grid_constant__ CUtensorMap tm_vl,
                 const __grid_constant__ AttnParams p, const __grid_constant__ PushParams push) {
     static_assert(kD == 64 || kD == 128, "head_dim 64 or 128");
-    static_assert(!kDebug || kD == 128, "the debug hooks exist for head_dim 128 only");
     constexpr int kAtoms = kD / 64;                    // 64-element swizzle atoms per row
     constexpr int kOperandBytes = kAtoms * kHalfBytes; // bytes one Q / K / V tile occupies
     extern __shared__ uint8_t smem_raw[];
@@ -184,9 +261,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(smem_u32(&ctl->s_full[t]), 1);
-            mbar_init(smem_u32(&ctl->p_full[t][0]), 128);
-            mbar_init(smem_u32(&ctl->p_full[t][1]), 128);
-            mbar_init(smem_u32(&ctl->o_done[t]), 1);
+            for (int c = 0; c < kPieces; ++c) {
+                mbar_init(smem_u32(&ctl->p_full[t][c]), kTileM);
+                mbar_init(smem_u32(&ctl->o_done[t][c]), 1);
+            }
         }
         mbar_init(smem_u32(&ctl->teardown), 1);
         mbar_init_fence();
@@ -261,9 +339,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     }
 
-    // Registers move from the control warpgroup to the softmax warpgroups. Each role's code is
-    // dominated by its own setmaxnreg so that the register allocator budgets the regions
-    // separately.
     if (warp >= kSoftmaxWarps) setmaxnreg_dec<kRegsControl>();
     if (warp == kTmaWarp) {
         // =============================== TMA producer ======================================
@@ -311,11 +386,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     const uint32_t ph = (j >> 1) & 1;
                     const uint32_t bk = smem_u32(&ctl->k_full[st]);
                     const uint32_t bv = smem_u32(&ctl->v_full[st]);
+                    dbg_stamp(p, 3, j, 0, true);
                     if (j >= kStages) {
                         ok = mbar_wait(smem_u32(&ctl->k_empty[st]), ph ^ 1, s_abort, p.status,
                                        pipe_limit, PA_DEV_TIMEOUT_PIPE);
                         if (!ok) break;
                     }
+                    dbg_stamp(p, 3, j, 1, true);
                     mbar_expect_tx(bk, kOperandBytes);
                     tma_load_5d(sK + st * kTileBytes, mk, bk, 0, t * kTileN, hk, bidx, ck);
                     if (kAtoms == 2)
@@ -328,6 +405,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                             break;
                         }
                     }
+                    dbg_stamp(p, 3, j, 2, true);
                     mbar_expect_tx(bv, kOperandBytes);
                     tma_load_5d(sV + st * kTileBytes, mv, bv, 0, t * kTileN, hk, bidx, ck);
                     if (kAtoms == 2)
@@ -350,49 +428,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
     } else if (warp == kMmaWarp) {
         // =============================== MMA issuer ========================================
-        // The issuer must keep ahead of the tensor core (64 cycles per 128x128x16 MMA): the
-        // k-step loops are unrolled and every descriptor is a base plus a constant.
-        if (lane == 0 && n_tiles > 0) {
+        // The issuer must keep ahead of the tensor core (64 cycles per 128x128x16 MMA). All 32
+        // lanes of the warp run this code in lockstep and every tcgen05.mma / tcgen05.commit is
+        // predicated on one elected lane: control flow and descriptor arithmetic stay
+        // warp-uniform, which costs about 24 cycles per issued MMA where a single lane running
+        // the loop alone (a divergent region) needs 55 to 75 and falls behind the tensor core.
+        // The k-step loops are unrolled and every descriptor is a base plus a constant.
+        if (n_tiles > 0) {
             constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN);
             constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kD);
-            constexpr uint32_t idesc_pv64 = make_idesc_f16(kBF16, true, kTileM, 64);
-            const uint32_t v_lbo = kDebug ? static_cast<uint32_t>(p.v_lbo) : kHalfBytes;
-            const uint32_t v_sbo = kDebug ? static_cast<uint32_t>(p.v_sbo) : 1024u;
-            const bool pv_split = kDebug ? (p.pv_split != 0) : false;
+            const uint32_t leader = elect_one() ? 1u : 0u;
+            const bool stamper = (lane == 0);
 
             // Descriptors differ from a per-operand base only in the start-address field (units
-            // of 16 bytes).
+            // of 16 bytes, bits 0-13 of the low word; shared memory ends below 2^18, so adding
+            // never carries out of the field): one high word per operand kind, 32-bit arithmetic
+            // on the low words.
             const uint64_t dq0 = smem_desc_sw128(sQ, 16, 1024);
-            const uint64_t dk0 = smem_desc_sw128(sK, 16, 1024);
-            const uint64_t dv0 = smem_desc_sw128(sV, v_lbo, v_sbo);
+            const uint64_t dv0 = smem_desc_sw128(sV, kHalfBytes, 1024);
+            const uint32_t hi_qk = static_cast<uint32_t>(dq0 >> 32);
+            const uint32_t hi_v = static_cast<uint32_t>(dv0 >> 32);
+            const uint32_t lo_q = static_cast<uint32_t>(dq0);
+            const uint32_t lo_k = static_cast<uint32_t>(smem_desc_sw128(sK, 16, 1024));
+            const uint32_t lo_v = static_cast<uint32_t>(dv0);
             auto issue_qk = [&](int t, int st) {
-                const uint64_t a0 = dq0 + static_cast<uint64_t>((t * kTileBytes) >> 4);
-                const uint64_t b0 = dk0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
+                const uint32_t a0 = lo_q + ((t * kTileBytes) >> 4);
+                const uint32_t b0 = lo_k + ((st * kTileBytes) >> 4);
                 const uint32_t d = tmem + kColS0 + t * kTileN;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
-                    tc_mma_ss(d, a0 + off, b0 + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
+                    tc_mma_ss_elect(d, a0 + off, hi_qk, b0 + off, hi_qk, idesc_qk, ks > 0 ? 1u : 0u, leader);
                 }
             };
-            // P V for key rows [64*half, 64*half+64) of the tile: four k-steps
-            auto issue_pv_half = [&](int t, int st, int half, bool acc) {
-                const uint64_t b0 = dv0 + static_cast<uint64_t>((st * kTileBytes) >> 4);
+            // P V for key rows [32*piece, 32*piece+32) of the tile: two k-steps of 16 keys. The
+            // piece's probabilities sit at S columns [16*piece, 16*piece+16), 8 columns per k-step.
+            auto issue_pv_piece = [&](int t, int st, int piece, bool acc) {
+                const uint32_t b0 = lo_v + ((st * kTileBytes) >> 4);
                 const uint32_t a0 = tmem + kColS0 + t * kTileN;
                 const uint32_t d = tmem + kColO0 + t * kD;
 #pragma unroll
-                for (int k4 = 0; k4 < 4; ++k4) {
-                    const int ks = half * 4 + k4;
-                    const uint64_t b = b0 + static_cast<uint64_t>((ks * 16 * 128) >> 4);
+                for (int k2 = 0; k2 < 2; ++k2) {
+                    const int ks = piece * 2 + k2;
+                    const uint32_t b = b0 + ((ks * 16 * 128) >> 4);
                     const uint32_t accum = (acc || ks > 0) ? 1u : 0u;
-                    // P of column half h lives at S columns [64h, 64h+32): 8 columns per k-step
-                    const uint32_t a = a0 + half * 64 + k4 * 8;
-                    if (!pv_split) {
-                        tc_mma_ts(d, a, b, idesc_pv, accum);
-                    } else {
-                        tc_mma_ts(d, a, b, idesc_pv64, accum);
-                        tc_mma_ts(d + 64, a, b + static_cast<uint64_t>(kHalfBytes >> 4), idesc_pv64, accum);
-                    }
+                    tc_mma_ts_elect(d, a0 + ks * 8, b, hi_v, idesc_pv, accum, leader);
                 }
             };
 
@@ -400,13 +480,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                 PA_DEV_TIMEOUT_PIPE);
             ok = ok && mbar_wait(smem_u32(&ctl->k_full[0]), 0, s_abort, p.status, pipe_limit,
                                  PA_DEV_TIMEOUT_PIPE);
+            ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after();
                 issue_qk(0, 0);
-                tc_commit(smem_u32(&ctl->s_full[0]));
+                tc_commit_elect(smem_u32(&ctl->s_full[0]), leader);
                 issue_qk(1, 0);
-                tc_commit(smem_u32(&ctl->s_full[1]));
-                tc_commit(smem_u32(&ctl->k_empty[0]));
+                tc_commit_elect(smem_u32(&ctl->s_full[1]), leader);
+                tc_commit_elect(smem_u32(&ctl->k_empty[0]), leader);
             }
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int st = j & 1;
@@ -414,42 +495,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const int stn = (j + 1) & 1;
                 const uint32_t phn = ((j + 1) >> 1) & 1;
                 const bool more = (j + 1 < n_tiles);
+                dbg_stamp(p, 4, j, 0, stamper);
                 ok = mbar_wait(smem_u32(&ctl->v_full[st]), ph, s_abort, p.status, pipe_limit,
                                PA_DEV_TIMEOUT_PIPE);
+                dbg_stamp(p, 4, j, 1, stamper);
                 if (ok && more)
                     ok = mbar_wait(smem_u32(&ctl->k_full[stn]), phn, s_abort, p.status, pipe_limit,
                                    PA_DEV_TIMEOUT_PIPE);
+                dbg_stamp(p, 4, j, 2, stamper);
+                // (every lane polls the same barriers; the vote keeps the warp in one piece when a
+                // wait gives up in some lanes only)
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
-                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 0, true);
-                    ok = mbar_wait(smem_u32(&ctl->p_full[t][0]), j & 1, s_abort, p.status, pipe_limit,
-                                   PA_DEV_TIMEOUT_PIPE);
+                    dbg_stamp(p, 2, j, t * 4 + 0, stamper);
+#pragma unroll
+                    for (int c = 0; c < kPieces; ++c) {
+                        ok = mbar_wait(smem_u32(&ctl->p_full[t][c]), j & 1, s_abort, p.status, pipe_limit,
+                                       PA_DEV_TIMEOUT_PIPE);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        if (c == 0) dbg_stamp(p, 2, j, t * 4 + 1, stamper);
+                        tc_fence_after();
+                        issue_pv_piece(t, st, c, j > 0);
+                        // one barrier per piece (one phase per tile each): a softmax warp that has to
+                        // rescale O in the middle of a tile waits for the last piece issued so far
+                        tc_commit_elect(smem_u32(&ctl->o_done[t][c]), leader);
+                    }
                     if (!ok) break;
-                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 1, true);
-                    tc_fence_after();
-                    issue_pv_half(t, st, 0, j > 0);
-                    ok = mbar_wait(smem_u32(&ctl->p_full[t][1]), j & 1, s_abort, p.status, pipe_limit,
-                                   PA_DEV_TIMEOUT_PIPE);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv_half(t, st, 1, j > 0);
-                    tc_commit(smem_u32(&ctl->o_done[t]));
-                    if (t == 1) tc_commit(smem_u32(&ctl->v_empty[st]));
-                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 2, true);
+                    if (t == 1) tc_commit_elect(smem_u32(&ctl->v_empty[st]), leader);
+                    dbg_stamp(p, 2, j, t * 4 + 2, stamper);
                     if (more) {
                         issue_qk(t, stn);
-                        tc_commit(smem_u32(&ctl->s_full[t]));
-                        if (t == 1) tc_commit(smem_u32(&ctl->k_empty[stn]));
+                        tc_commit_elect(smem_u32(&ctl->s_full[t]), leader);
+                        if (t == 1) tc_commit_elect(smem_u32(&ctl->k_empty[stn]), leader);
                     }
-                    dbg_stamp<kDebug>(p, 2, j, t * 4 + 3, true);
+                    dbg_stamp(p, 2, j, t * 4 + 3, stamper);
                 }
             }
             if (!ok) {
                 // Nothing may still be running on the tensor core when TMEM is released.
                 int none = 0;
                 volatile int* no_abort = &none;
-                tc_commit(smem_u32(&ctl->teardown));
+                tc_commit_elect(smem_u32(&ctl->teardown), leader);
                 mbar_wait(smem_u32(&ctl->teardown), 0, no_abort, nullptr, 100000000ull, 0);
             }
         }
@@ -457,21 +546,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // =============================== softmax + epilogue ================================
         setmaxnreg_inc<kRegsSoftmax>();
         const int quarter = warp & 3;
-        const int t = (warp >> 2) & 1;
-        const int half = warp >> 3;
+        const int t = warp >> 2;
         const int row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN + half * 64;  // my 64 logit columns
-        const uint32_t tO = tmem + lane_base + kColO0 + t * kD + half * (kD / 2);  // my half of the output columns
+        const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN;  // my row's 128 logits
+        const uint32_t tO = tmem + lane_base + kColO0 + t * kD;      // my row of the output
         const uint32_t bs = smem_u32(&ctl->s_full[t]);
-        const uint32_t bp = smem_u32(&ctl->p_full[t][half]);
-        const uint32_t bo = smem_u32(&ctl->o_done[t]);
-        const int pair_bar = 1 + t * 4 + quarter;
         const float sl = p.scale_log2;
-        const bool stamper = (quarter == 0 && lane == 0 && half == 0);
+        const bool stamper = (quarter == 0 && lane == 0);
 
-        float m_ref = -INFINITY;
-        float l_sum = 0.f;  // over my columns only
+        float m_ref = -INFINITY;  // the reference my row's probabilities and O are scaled by
+        float l_sum = 0.f;
         bool ok = true;
         int j = 0;
         const long long q_here = kCausal ? p.q_pos[qc] + row0 + t * kTileM + row_in_tile : 0;  // my row's global position
@@ -480,163 +565,101 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (c_kv >= p.n_kv_chunks) c_kv -= p.n_kv_chunks;
             const int tiles_c = tiles_in_chunk(c_kv);
             for (int tk = 0; tk < tiles_c; ++tk, ++j) {
-                int valid = min(kTileN, p.kv_rows - tk * kTileN) - half * 64;  // of my 64 columns
+                // which of the tile's 128 key columns count for my row: the key mask words (the
+                // same for the whole warp), cut at the ragged end of the chunk and at the causal
+                // diagonal
+                const int exist = min(kTileN, p.kv_rows - tk * kTileN);
+                int valid = exist;
                 if (kCausal) {
-                    const long long lim = q_here - (p.kv_pos[c_kv] + tk * kTileN + half * 64) + 1;
+                    const long long lim = q_here - (p.kv_pos[c_kv] + tk * kTileN) + 1;
                     valid = static_cast<int>(lim < valid ? (lim < 0 ? 0 : lim) : valid);
                 }
-                // which of my 64 columns count: the key mask word (same for the whole warp), cut
-                // at the ragged end of the chunk and at the causal diagonal
-                unsigned long long live = ~0ull;
-                if (p.key_bits != nullptr && valid > 0)  // (a half tile past the chunk's end has no word)
-                    live = __ldg(p.key_bits + bidx * p.kb_sb + c_kv * p.kb_sc + tk * 2 + half);
-                if (valid < 64) live &= (valid <= 0) ? 0ull : ((1ull << valid) - 1ull);
-                dbg_stamp<kDebug>(p, t, j, 0, stamper);
-                // A wait that gives up does not leave the loop: the two partner warps must meet at
-                // every pair barrier below, and once the abort word is set no wait blocks any more.
+                unsigned long long kw[2] = {~0ull, ~0ull};
+                if (p.key_bits != nullptr) {  // (a half tile past the chunk's end has no word)
+                    const unsigned long long* w = p.key_bits + bidx * p.kb_sb + c_kv * p.kb_sc + tk * 2;
+                    kw[0] = __ldg(w);
+                    if (exist > 64) kw[1] = __ldg(w + 1);
+                }
+                const bool plain = (valid == kTileN) && (p.key_bits == nullptr);
+                dbg_stamp(p, t, j, 0, stamper);
+                // A wait that gives up does not leave the loop: once the abort word is set no wait
+                // blocks any more, and the arrivals below keep the other roles moving.
                 ok = mbar_wait(bs, j & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
-                dbg_stamp<kDebug>(p, t, j, 1, stamper);
+                dbg_stamp(p, t, j, 1, stamper);
                 tc_fence_after();
-                // Pass 1: row maximum of my 64 logits. The logits are not kept: pass 2 reads them
-                // again from TMEM 32 columns at a time, which keeps the thread within its register
-                // budget (TMEM bandwidth is plentiful, registers are not).
-                float mx[2];
-                {
-                    uint32_t s[2][32];
-                    tmem_ld32(tS, s[0]);
-                    tmem_ld32(tS + 32, s[1]);
-                    tc_wait_ld();
-                    tmem_ld_fence(s[0]);
-                    tmem_ld_fence(s[1]);
-                    dbg_stamp<kDebug>(p, t, j, 2, stamper);
-                    if (kDebug && p.dbg_s != nullptr && blockIdx.x == 0) {
-                        float* d = p.dbg_s + ((static_cast<size_t>(t) * n_tiles + j) * 128 + row_in_tile) * 128 + half * 64;
+                const bool plain_warp = __all_sync(0xffffffffu, plain);
+                uint32_t buf[2][32];
+                tmem_ld32(tS, buf[0]);
 #pragma unroll
-                        for (int c = 0; c < 2; ++c)
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) d[c * 32 + i] = __uint_as_float(s[c][i]);
-                    }
-                    if (live != ~0ull) {
-#pragma unroll
-                        for (int c = 0; c < 2; ++c)
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (((live >> (c * 32 + i)) & 1ull) == 0) s[c][i] = 0xff800000u;  // -inf
-                    }
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        mx[c] = fmaxf(__uint_as_float(s[c][0]), __uint_as_float(s[c][1]));
-#pragma unroll
-                        for (int i = 2; i < 32; i += 2)
-                            mx[c] = fmax3(mx[c], __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
-                    }
-                }
-                // row maximum over both column halves: swap partial maxima with the partner thread
-                const float mine = fmaxf(mx[0], mx[1]);
-                ctl->xch[j & 1][t][half][row_in_tile] = mine;
-                pair_sync(pair_bar);
-                const float m_new = fmax3(mine, ctl->xch[j & 1][t][half ^ 1][row_in_tile], m_ref);
-                const bool grow = (m_new - m_ref) * sl > kRescaleThreshold;
-                if (__any_sync(0xffffffffu, grow)) {  // same decision in both partner warps
-                    // (a row that has seen no visible key yet keeps m = -inf: scale by 1, not by NaN)
-                    const float alpha = (m_new == -INFINITY) ? 1.0f : ex2_approx((m_ref - m_new) * sl);
-                    l_sum *= alpha;
-                    m_ref = m_new;
-                    if (j > 0) {
-                        ok = mbar_wait(bo, (j - 1) & 1, s_abort, p.status, pipe_limit,
-                                       PA_DEV_TIMEOUT_PIPE) && ok;
-                        tc_fence_after();
-#pragma unroll
-                        for (int c = 0; c < kAtoms; ++c) {
-                            uint32_t o[32];
-                            tmem_ld32(tO + c * 32, o);
-                            tc_wait_ld();
-                            tmem_ld_fence(o);
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            tmem_st32(tO + c * 32, o);
-                        }
-                        // P V of this step adds to all 128 output columns as soon as the first
-                        // half of P is handed over: both halves of O must be rescaled by then.
-                        tc_wait_st();
-                        tc_fence_before();
-                        pair_sync(pair_bar);
-                        tc_fence_after();
-                    }
-                }
-                const float neg = (m_ref == -INFINITY) ? 0.0f : -m_ref * sl;
-                dbg_stamp<kDebug>(p, t, j, 3, stamper);
-                // p = 2^(s*sl - m*sl) in packed fp32x2 arithmetic. The exponentials are split between
-                // the special-function unit and an FMA-pipe polynomial so that neither pipe alone
-                // bounds the softmax: either the warps of column half 1 take the polynomial for all
-                // their elements (kPolyHalf1) or kPolyPairsOf8 of every 8 element pairs do.
-                const float2 sl2 = make_float2(sl, sl);
-                const float2 neg2 = make_float2(neg, neg);
-                // Pass 2, per 32-column chunk: reload, exponentiate, pack, and store the 16 packed
-                // words over logit columns of my own that are already consumed (chunk c goes to my
-                // columns [16c, 16c+16)), so partner threads never touch each other's columns.
-                float2 ls[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t sc[32];
-                    tmem_ld32(tS + c * 32, sc);
+                for (int c = 0; c < kPieces; ++c) {
+                    uint32_t(&sc)[32] = buf[c & 1];
                     tc_wait_ld();
                     tmem_ld_fence(sc);
-                    if (live != ~0ull) {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (((live >> (c * 32 + i)) & 1ull) == 0) sc[i] = 0xff800000u;  // -inf
-                    }
+                    if (c + 1 < kPieces) tmem_ld32(tS + (c + 1) * kPieceCols, buf[(c + 1) & 1]);
+                    uint32_t live = 0xffffffffu;
                     uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float2 x = __ffma2_rn(
-                            make_float2(__uint_as_float(sc[i]), __uint_as_float(sc[i + 1])), sl2, neg2);
-                        float2 e;
-                        if (kPolyHalf1 ? (half == 1) : (((i >> 1) & 7) < kPolyPairsOf8)) {
-                            e = exp2_poly2(x);
-                        } else {
-                            e.x = ex2_approx(x.x);
-                            e.y = ex2_approx(x.y);
-                        }
-                        ls[c] = __fadd2_rn(ls[c], e);
-                        pk[i >> 1] = kBF16 ? pack_bf16x2(e.x, e.y) : pack_f16x2(e.x, e.y);
+                    float ls, mx;
+                    const float neg = (m_ref == -INFINITY) ? 0.0f : -m_ref * sl;
+                    if (plain_warp) {
+                        softmax_chunk<kBF16, false>(sc, live, sl, neg, pk, ls, mx);
+                    } else {
+                        const int v = valid - c * kPieceCols;
+                        live = (v >= 32) ? 0xffffffffu : (v <= 0 ? 0u : ((1u << v) - 1u));
+                        live &= static_cast<uint32_t>(kw[c >> 1] >> ((c & 1) * 32));
+                        softmax_chunk<kBF16, true>(sc, live, sl, neg, pk, ls, mx);
                     }
-                    tmem_st16(tS + c * 16, pk);
+                    // The previous piece is handed over only now, behind this piece's exponentials
+                    // in program order: its store has long landed, so the wait costs nothing and
+                    // the special-function unit is never left idle for a round trip to TMEM.
+                    if (c > 0) {
+                        tc_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&ctl->p_full[t][c - 1]));
+                        dbg_stamp(p, t, j, 1 + c, stamper);
+                    }
+                    // (m_ref = mx = -inf: NaN > threshold is false, the row stays empty)
+                    const bool grow = (mx - m_ref) * sl > kRescaleThreshold;
+                    if (__any_sync(0xffffffffu, grow)) {
+                        // every P V handed over so far must have been added to O before O is
+                        // rescaled: the last one is waited for (MMAs complete in order)
+                        const uint32_t bo = (c > 0) ? smem_u32(&ctl->o_done[t][c - 1])
+                                                    : smem_u32(&ctl->o_done[t][kPieces - 1]);
+                        const uint32_t par = (c > 0) ? (j & 1) : ((j - 1) & 1);
+                        const float2 r = softmax_piece_regrow<kBF16, kD>(
+                            tS + c * kPieceCols, tS + c * (kPieceCols / 2), tO, live, sl, mx, m_ref, l_sum, j > 0 || c > 0,
+                            bo, par, s_abort, p.status, pipe_limit);
+                        m_ref = r.x;
+                        l_sum = r.y;
+                    } else {
+                        l_sum += ls;
+                        // P of key columns [32c, 32c+32) over S columns [16c, 16c+16): consumed by now
+                        tmem_st16(tS + c * (kPieceCols / 2), pk);
+                    }
                 }
-                {
-                    const float2 a = __fadd2_rn(ls[0], ls[1]);
-                    l_sum += a.x + a.y;
-                }
-                dbg_stamp<kDebug>(p, t, j, 4, stamper);
                 tc_wait_st();
                 tc_fence_before();
-                mbar_arrive(bp);
-                dbg_stamp<kDebug>(p, t, j, 5, stamper);
+                mbar_arrive(smem_u32(&ctl->p_full[t][kPieces - 1]));
+                dbg_stamp(p, t, j, 1 + kPieces, stamper);
             }
         }
         // (a CTA whose queries see no key at all writes zeros and an LSE of -inf)
         const bool empty = (n_tiles == 0);
         if (!empty)
-            ok = mbar_wait(bo, (n_tiles - 1) & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
-        // row sum over both halves
-        ctl->xch[n_tiles & 1][t][half][row_in_tile] = l_sum;
-        pair_sync(pair_bar);
-        const float l_row = l_sum + ctl->xch[n_tiles & 1][t][half ^ 1][row_in_tile];
+            ok = mbar_wait(smem_u32(&ctl->o_done[t][kPieces - 1]), (n_tiles - 1) & 1, s_abort, p.status, pipe_limit,
+                           PA_DEV_TIMEOUT_PIPE) && ok;
         if (ok) {
             tc_fence_after();
             const int row = row0 + t * kTileM + row_in_tile;
             const bool in_range = row < p.q_rows;
             // a row that saw no key (all masked) comes out as zeros with an LSE of -inf
-            const float inv = (empty || !(l_row > 0.0f)) ? 0.0f : 1.0f / l_row;
+            const float inv = (empty || !(l_sum > 0.0f)) ? 0.0f : 1.0f / l_sum;
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
                              (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
-                              static_cast<long long>(row) * p.o_ss) + half * (kD / 2);
+                              static_cast<long long>(row) * p.o_ss);
 #pragma unroll
-            for (int c = 0; c < kAtoms; ++c) {
+            for (int b = 0; b < kD / 32; ++b) {
                 uint32_t o[32];
-                tmem_ld32(tO + c * 32, o);
+                tmem_ld32(tO + b * 32, o);
                 tc_wait_ld();
                 tmem_ld_fence(o);
                 if (empty) {
@@ -651,16 +674,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const float a = __uint_as_float(o[v4 * 8 + 2 * i]) * inv;
-                            const float b = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
-                            wp[i] = kBF16 ? pack_bf16x2(a, b) : pack_f16x2(a, b);
+                            const float b2 = __uint_as_float(o[v4 * 8 + 2 * i + 1]) * inv;
+                            wp[i] = kBF16 ? pack_bf16x2(a, b2) : pack_f16x2(a, b2);
                         }
-                        *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = w;
+                        *reinterpret_cast<uint4*>(orow + b * 32 + v4 * 8) = w;
                     }
                 }
             }
-            if (half == 0 && in_range && p.lse[qc] != nullptr) {
+            if (in_range && p.lse[qc] != nullptr) {
                 p.lse[qc][static_cast<long long>(bidx) * p.l_sb + static_cast<long long>(head) * p.l_sh + row] =
-                    m_ref * p.scale + __logf(l_row);
+                    m_ref * p.scale + __logf(l_sum);
             }
         }
     }

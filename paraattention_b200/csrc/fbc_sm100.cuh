@@ -108,7 +108,8 @@ fbc_residual_diff_kernel(const uint4* __restrict__ h1, const uint4* __restrict__
     float acc_d = 0.f, acc_p = 0.f;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += stride) {
-        const uint4 a = __ldg(h1 + i), b = __ldg(h0 + i);
+        // (h0 == nullptr: the residual is h1 itself, i.e. the caller compares two given tensors)
+        const uint4 a = __ldg(h1 + i), b = h0 != nullptr ? __ldg(h0 + i) : make_uint4(0, 0, 0, 0);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
         uint32_t cw[4];
         float cur[8];
@@ -148,7 +149,7 @@ fbc_residual_diff_strided_kernel(const uint16_t* __restrict__ h1, const uint16_t
         const long long r = i / cols_ds;
         const int c = static_cast<int>(i % cols_ds) * ds;
         const long long src = r * cols + c;
-        const float cur = round16<kBF16>(lo16<kBF16>(h1[src]) - lo16<kBF16>(h0[src]));
+        const float cur = round16<kBF16>(lo16<kBF16>(h1[src]) - (h0 != nullptr ? lo16<kBF16>(h0[src]) : 0.f));
         if (prev != nullptr) {
             const float p = lo16<kBF16>(prev[i]);
             acc_d += fabsf(round16<kBF16>(p - cur));
@@ -175,6 +176,18 @@ fbc_axpy_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4*
             ow[k] = pack16<kBF16>(l, h);
         }
         __stcs(out + i, make_uint4(ow[0], ow[1], ow[2], ow[3]));
+    }
+}
+
+// The same for sizes or addresses the 16-byte form cannot take: one element per thread iteration.
+template <bool kBF16, bool kSub>
+__global__ void __launch_bounds__(kFbcThreads)
+fbc_axpy_scalar_kernel(const uint16_t* __restrict__ a, const uint16_t* __restrict__ b, uint16_t* __restrict__ out,
+                       long long n) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float x = lo16<kBF16>(a[i]), y = lo16<kBF16>(b[i]);
+        out[i] = static_cast<uint16_t>(pack16<kBF16>(kSub ? x - y : x + y, 0.f) & 0xffffu);
     }
 }
 

@@ -28,6 +28,20 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
+// Streaming multiprocessors of the current device (cached per device): grid caps of the
+// grid-stride kernels are multiples of it.
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -77,10 +91,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int head_dim, int ro
     return PA_OK;
 }
 
-template <bool kBF16, bool kDebug, bool kCausal, int kD>
+template <bool kBF16, bool kCausal, int kD>
 int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream) {
-    auto kern = pa::attn_fwd_kernel<kBF16, kDebug, kCausal, kD>;
+    auto kern = pa::attn_fwd_kernel<kBF16, kCausal, kD>;
     static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
     {
@@ -99,17 +113,15 @@ int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa:
     return PA_OK;
 }
 
-template <bool kBF16, bool kDebug>
+template <bool kBF16>
 int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream, int head_dim) {
-    if (kDebug && (p.causal || head_dim != 128))
-        return fail(PA_ENOTSUP, "the debug hooks are built for non-causal head_dim 128 only");
     if (head_dim == 64) {
-        return p.causal ? launch_attn_inst<kBF16, false, true, 64>(maps, p, push, grid, stream)
-                        : launch_attn_inst<kBF16, false, false, 64>(maps, p, push, grid, stream);
+        return p.causal ? launch_attn_inst<kBF16, true, 64>(maps, p, push, grid, stream)
+                        : launch_attn_inst<kBF16, false, 64>(maps, p, push, grid, stream);
     }
-    if (p.causal) return launch_attn_inst<kBF16, false, true, 128>(maps, p, push, grid, stream);
-    return launch_attn_inst<kBF16, kDebug, false, 128>(maps, p, push, grid, stream);
+    return p.causal ? launch_attn_inst<kBF16, true, 128>(maps, p, push, grid, stream)
+                    : launch_attn_inst<kBF16, false, 128>(maps, p, push, grid, stream);
 }
 
 int check_common(int head_dim, int dtype, float scale) {
@@ -126,8 +138,7 @@ int out_checks(const void* out, const int64_t* o_stride) {
     return PA_OK;
 }
 
-int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, int v_sbo, int pv_split, bool debug,
-                  long long* dbg_t = nullptr, int dbg_steps = 0) {
+int attn_fwd_impl(const pa_attn_args* a, void* stream, long long* dbg_t = nullptr, int dbg_steps = 0) {
     if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
     if (!a->q || !a->k || !a->v || !a->out) return fail(PA_EINVAL, "q, k, v and out must be non-NULL");
     if (a->batch <= 0 || a->heads <= 0 || a->seq_q <= 0 || a->seq_kv <= 0)
@@ -174,12 +185,13 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     p.key_bits = reinterpret_cast<const unsigned long long*>(a->key_bits);
     p.kb_sb = (a->seq_kv + 63) / 64;
     p.kb_sc = 0;
-    p.dbg_s = dbg_s;
-    p.v_lbo = v_lbo;
-    p.v_sbo = v_sbo;
-    p.pv_split = pv_split;
+#if PA_TIMELINE
     p.dbg_t = dbg_t;
     p.dbg_steps = dbg_steps;
+#else
+    (void)dbg_t;
+    (void)dbg_steps;
+#endif
 
     const long long pairs = (a->seq_q + 255) / 256;
     const long long grid = pairs * a->heads * a->batch;
@@ -187,12 +199,8 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, float* dbg_s, int v_lbo, 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     pa::PushParams push;
     memset(&push, 0, sizeof(push));
-    if (debug) {
-        return a->dtype == PA_BF16 ? launch_attn<true, true>(maps, p, push, int(grid), s, a->head_dim)
-                                   : launch_attn<false, true>(maps, p, push, int(grid), s, a->head_dim);
-    }
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s, a->head_dim)
-                               : launch_attn<false, false>(maps, p, push, int(grid), s, a->head_dim);
+    return a->dtype == PA_BF16 ? launch_attn<true>(maps, p, push, int(grid), s, a->head_dim)
+                               : launch_attn<false>(maps, p, push, int(grid), s, a->head_dim);
 }
 
 int fill_push(const pa_cp_push_args* a, pa::PushParams* p) {
@@ -230,17 +238,17 @@ extern "C" {
 const char* pa_last_error(void) { return g_err; }
 int pa_version(void) { return 1; }
 
-int pa_attn_fwd(const pa_attn_args* args, void* stream) {
-    return attn_fwd_impl(args, stream, nullptr, 0, 0, 0, false);
-}
+int pa_attn_fwd(const pa_attn_args* args, void* stream) { return attn_fwd_impl(args, stream); }
 
-int pa_dbg_attn_fwd(const pa_attn_args* args, float* dbg_s, int v_lbo, int v_sbo, int pv_split, void* stream) {
-    return attn_fwd_impl(args, stream, dbg_s, v_lbo, v_sbo, pv_split, true);
+#if PA_TIMELINE
+// Profiling builds only (-DPA_TIMELINE=1; not declared in the public header, not in the shipped
+// library): pa_attn_fwd whose first CTA records clock64() stamps of its pipeline phases for the
+// first `steps` key/value tiles into stamps[5][steps][8] (softmax of query tile 0, of query
+// tile 1, MMA issuer, TMA producer, MMA operand waits).
+int pa_timeline_attn_fwd(const pa_attn_args* args, long long* stamps, int steps, void* stream) {
+    return attn_fwd_impl(args, stream, stamps, steps);
 }
-
-int pa_dbg_attn_timeline(const pa_attn_args* args, long long* stamps, int steps, void* stream) {
-    return attn_fwd_impl(args, stream, nullptr, pa::kHalfBytes, 1024, 0, PA_TIMELINE ? false : true, stamps, steps);
-}
+#endif
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     if (a == nullptr) return fail(PA_EINVAL, "args is NULL");
@@ -354,8 +362,8 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         push.n_push_ctas = n;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return a->dtype == PA_BF16 ? launch_attn<true, false>(maps, p, push, int(grid), s, a->head_dim)
-                               : launch_attn<false, false>(maps, p, push, int(grid), s, a->head_dim);
+    return a->dtype == PA_BF16 ? launch_attn<true>(maps, p, push, int(grid), s, a->head_dim)
+                               : launch_attn<false>(maps, p, push, int(grid), s, a->head_dim);
 }
 
 int pa_pack_key_mask(const uint8_t* mask, int64_t batch_stride, int32_t batch, int32_t n_chunks, int32_t rows,
@@ -365,7 +373,7 @@ int pa_pack_key_mask(const uint8_t* mask, int64_t batch_stride, int32_t batch, i
     if (batch_stride < int64_t(n_chunks) * rows) return fail(PA_EINVAL, "pack_key_mask: batch stride shorter than a row of keys");
     const long long total = static_cast<long long>(batch) * n_chunks * ((rows + 63) / 64);
     long long blocks = (total + 7) / 8;  // 8 warps per block
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > static_cast<long long>(sm_count()) * 8) blocks = static_cast<long long>(sm_count()) * 8;
     pa::pack_key_mask_kernel<<<int(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         mask, batch_stride, batch, n_chunks, rows, reinterpret_cast<unsigned long long*>(out));
     cudaError_t e = cudaGetLastError();
@@ -408,7 +416,7 @@ int pa_merge_out_lse(float* acc_out, float* acc_lse, const void* blk_out, const 
     if (rows <= 0 || d <= 0) return fail(PA_EINVAL, "merge: rows and d must be positive");
     const int threads = 256;
     long long blocks = (rows + 7) / 8;
-    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks > static_cast<long long>(sm_count()) * 16) blocks = static_cast<long long>(sm_count()) * 16;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (blk_dtype) {
         case 0: pa::merge_out_lse_kernel<0><<<int(blocks), threads, 0, s>>>(acc_out, acc_lse, blk_out, blk_lse, rows, d); break;
@@ -426,7 +434,7 @@ int64_t pa_fbc_scratch_bytes(void) { return int64_t(2 * pa::kFbcMaxBlocks) * 4 +
 int pa_fbc_residual_diff(const void* h1, const void* h0, const void* prev, void* new_resid, int64_t rows,
                          int32_t cols, int32_t downsample, int32_t dtype, float* result, void* scratch,
                          void* stream) {
-    if (!h1 || !h0 || !result || !scratch) return fail(PA_EINVAL, "fbc: h1, h0, result and scratch must be non-NULL");
+    if (!h1 || !result || !scratch) return fail(PA_EINVAL, "fbc: h1, result and scratch must be non-NULL");
     if (rows <= 0 || cols <= 0 || downsample < 1) return fail(PA_EINVAL, "fbc: rows, cols must be positive and downsample >= 1");
     if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "fbc: dtype must be PA_BF16 or PA_F16");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -484,7 +492,7 @@ static std::mutex g_fbc_static_mu;
 
 int pa_fbc_residual_diff_static(const void* h1, const void* h0, const void* prev, void* new_resid, int64_t rows,
                                 int32_t cols, int32_t downsample, int32_t dtype, float* result, void* stream) {
-    if (!h1 || !h0 || !result) return fail(PA_EINVAL, "fbc static: h1, h0 and result must be non-NULL");
+    if (!h1 || !result) return fail(PA_EINVAL, "fbc static: h1 and result must be non-NULL");
     if (rows <= 0 || cols <= 0 || downsample < 1)
         return fail(PA_EINVAL, "fbc static: rows, cols must be positive and downsample >= 1");
     if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "fbc static: dtype must be PA_BF16 or PA_F16");
@@ -549,14 +557,35 @@ int pa_fbc_residual_diff_static(const void* h1, const void* h0, const void* prev
 
 int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t sub, int32_t dtype, void* stream) {
     if (!a || !b || !out) return fail(PA_EINVAL, "axpy: NULL pointer");
-    if (numel <= 0 || numel % 8 != 0) return fail(PA_EINVAL, "axpy: numel must be a positive multiple of 8");
-    if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15u)
-        return fail(PA_EINVAL, "axpy: pointers must be 16-byte aligned");
+    if (numel <= 0) return fail(PA_EINVAL, "axpy: numel must be positive");
     if (dtype != PA_BF16 && dtype != PA_F16) return fail(PA_EINVAL, "axpy: dtype must be PA_BF16 or PA_F16");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool vec = numel % 8 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    if (!vec) {
+        // odd sizes or addresses: one 16-bit element per thread iteration
+        if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 1u)
+            return fail(PA_EINVAL, "axpy: pointers must be 2-byte aligned");
+        long long blocks = (numel + pa::kFbcThreads - 1) / pa::kFbcThreads;
+        const long long cap = static_cast<long long>(sm_count()) * 16;
+        if (blocks > cap) blocks = cap;
+        const uint16_t *sa = static_cast<const uint16_t*>(a), *sb = static_cast<const uint16_t*>(b);
+        uint16_t* so = static_cast<uint16_t*>(out);
+        if (dtype == PA_BF16) {
+            if (sub) pa::fbc_axpy_scalar_kernel<true, true><<<int(blocks), pa::kFbcThreads, 0, s>>>(sa, sb, so, numel);
+            else pa::fbc_axpy_scalar_kernel<true, false><<<int(blocks), pa::kFbcThreads, 0, s>>>(sa, sb, so, numel);
+        } else {
+            if (sub) pa::fbc_axpy_scalar_kernel<false, true><<<int(blocks), pa::kFbcThreads, 0, s>>>(sa, sb, so, numel);
+            else pa::fbc_axpy_scalar_kernel<false, false><<<int(blocks), pa::kFbcThreads, 0, s>>>(sa, sb, so, numel);
+        }
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(PA_ECUDA, "axpy launch: %s", cudaGetErrorString(e));
+        return PA_OK;
+    }
     const long long n8 = numel / 8;
     long long blocks = (n8 + pa::kFbcThreads - 1) / pa::kFbcThreads;
-    if (blocks > 148 * 16) blocks = 148 * 16;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
     const uint4 *pa_ = static_cast<const uint4*>(a), *pb_ = static_cast<const uint4*>(b);
     uint4* po = static_cast<uint4*>(out);
     if (dtype == PA_BF16) {
@@ -580,7 +609,8 @@ int taylor_checks(const char* what, int64_t numel, int32_t dtype) {
 bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 int taylor_blocks(long long n8) {
     long long blocks = (n8 + pa::kFbcThreads - 1) / pa::kFbcThreads;
-    return int(blocks > 148 * 16 ? 148 * 16 : blocks);
+    const long long cap = static_cast<long long>(sm_count()) * 16;
+    return int(blocks > cap ? cap : blocks);
 }
 }  // namespace
 
