@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the context-parallel attention hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference_gpu]
                     [--heads H] [--seq S] [--mesh UxR]
 
 One "step" is one non-causal bf16 attention over the whole sequence (B=1, D=128) of the
@@ -11,8 +11,21 @@ per GPU) the sequence is sharded over a ulysses x ring mesh and every step is on
 ``ulysses_attn_func`` / ``ring_attn_func`` / ``UnifiedAttnMode``; total work is fixed, so
 scaling is "strong". Prints ONE JSON line (rank 0).
 
-``--impl reference`` times the CPU restatement of the reference path (oracle/) on the host
-cores on a bounded sample of the same workload; under torchrun only rank 0 works.
+``--impl reference`` times the reference's CPU path on the host cores on a bounded sample of the
+same workload (at world size 1 that path is PyTorch's CPU scaled_dot_product_attention in fp32;
+the numpy oracle under oracle/ is the parity checker, not the timed baseline); under torchrun
+only rank 0 works.
+
+``--impl reference_gpu`` is the comparator on the same GPUs: the reference's own GPU path -
+PyTorch's SDPA library kernels (flash and cuDNN backends timed separately), NCCL all-to-alls
+for the Ulysses exchange and PyTorch's ring-attention loop - on the same inputs, meshes and
+timing harness. With ``--ref DIR`` (a directory holding the ``para_attn`` package) the
+reference's functions themselves are called; without it the same sequence of library calls is
+issued from this file (the reference adds nothing to them but the orchestration).
+
+Every line of the ``ours`` arm also carries ``parity``: after the timed region 1024 sampled
+output rows per rank (512 in each of two heads) are compared with the fp32 numpy oracle over
+all keys.
 """
 from __future__ import annotations
 
@@ -39,7 +52,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"])
+    ap.add_argument("--ref", default=None, help="reference_gpu: directory that holds the para_attn package")
+    ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row comparison with the oracle")
     ap.add_argument("--heads", type=int, default=24)
     ap.add_argument("--seq", type=int, default=32760)
     ap.add_argument("--mesh", default=None, help="UxR, default Nx1 (all Ulysses)")
@@ -95,27 +110,41 @@ def make_inputs(H, S, seed=0):
 # ------------------------------------------------------------------------------------------
 # CPU baseline / reference arm: the oracle on the host cores
 # ------------------------------------------------------------------------------------------
-def cpu_sample(H, S, budget_s=12.0):
-    """Time oracle attention for a slab of query rows of one head against all S keys; grow
-    the slab until about budget_s seconds of CPU work were spent. Returns (TFLOP/s, text)."""
-    import numpy as np
+def cpu_sample(H, S, budget_s=12.0, ref_dir=None):
+    """Time the reference's CPU path for a slab of query rows of one head against all S keys, fp32,
+    on all host cores; grow the slab until about budget_s seconds of CPU work were spent. At world
+    size 1 that path is one call of PyTorch's CPU scaled_dot_product_attention
+    (src/para_attn/para_attn_interface.py:111-119): with the reference package at hand
+    (``ref_dir``) its ``ulysses_attn_func`` is called, otherwise the library call it makes.
+    Returns (TFLOP/s, sample text, kind)."""
+    import torch
+    import torch.nn.functional as F
 
-    from oracle import cp_attention_oracle as O
+    fn, kind, what = F.scaled_dot_product_attention, "port", "torch CPU SDPA (the call the reference's world-1 path makes)"
+    for cand in ([ref_dir] if ref_dir else []) + [str(ROOT / "baseline" / "_ref")]:
+        if cand and (Path(cand) / "para_attn" / "__init__.py").exists():
+            sys.path.insert(0, str(cand))
+            import para_attn
 
-    rng = np.random.default_rng(0)
-    k = rng.standard_normal((1, 1, S, 128)).astype(np.float32) * 0.5
-    v = rng.standard_normal((1, 1, S, 128)).astype(np.float32) * 0.5
+            fn, kind, what = para_attn.ulysses_attn_func, "reference", "para_attn.ulysses_attn_func on CPU tensors"
+            break
+    g = torch.Generator().manual_seed(0)
+    k = torch.randn(1, 1, S, 128, generator=g) * 0.5
+    v = torch.randn(1, 1, S, 128, generator=g) * 0.5
     rows, spent, flops = 512, 0.0, 0.0
-    while spent < budget_s:
-        q = rng.standard_normal((1, 1, rows, 128)).astype(np.float32) * 0.5
-        t0 = time.perf_counter()
-        O.sdpa_with_lse(q, k, v)
-        dt = time.perf_counter() - t0
-        spent += dt
-        flops += 4.0 * rows * S * 128
-        if dt < 2.0 and rows < 8192:
-            rows *= 2
-    return flops / spent / 1e12, f"{int(flops / (4.0 * S * 128))} query rows of one head x all {S} keys, fp32 numpy oracle, {spent:.1f} s"
+    with torch.no_grad():
+        while spent < budget_s:
+            q = torch.randn(1, 1, rows, 128, generator=g) * 0.5
+            t0 = time.perf_counter()
+            fn(q, k, v)
+            dt = time.perf_counter() - t0
+            spent += dt
+            flops += 4.0 * rows * S * 128
+            if dt < 2.0 and rows < 16384:
+                rows *= 2
+    return (flops / spent / 1e12,
+            f"{int(flops / (4.0 * S * 128))} query rows of one head x all {S} keys, fp32, {what}, "
+            f"{torch.get_num_threads()} threads, {spent:.1f} s", kind)
 
 
 def run_reference(args):
@@ -125,11 +154,12 @@ def run_reference(args):
     H, S = args.heads, args.seq
     cores = os.cpu_count() or 1
     vals, sample = [], ""
+    kind = "port"
     for _ in range(args.warmup):
-        cpu_sample(H, S, budget_s=1.0)
+        cpu_sample(H, S, budget_s=1.0, ref_dir=args.ref)
     t_all = time.perf_counter()
     for _ in range(args.steps):
-        v, sample = cpu_sample(H, S, budget_s=max(2.0, 60.0 / max(args.steps, 1)))
+        v, sample, kind = cpu_sample(H, S, budget_s=max(2.0, 60.0 / max(args.steps, 1)), ref_dir=args.ref)
         vals.append(v)
     wall = time.perf_counter() - t_all
     value = statistics.mean(vals)
@@ -137,8 +167,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(H, S), "note": "CPU restatement of the reference path (oracle/), host cores"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(H, S), "note": "the reference's CPU path at world size 1, host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -279,23 +309,31 @@ def run_ours(args):
         sampler.start()  # early: nvidia-smi needs a moment before its first sample
     causal = VARIANT["causal"]
     q_h, k_h, v_h = make_inputs(H, S_pad)
+    parity_heads = sorted({1 % H, H - 2 if H > 2 else H - 1})
+    kv_full = {h: (k_h[0, h].float().numpy().copy(), v_h[0, h].float().numpy().copy()) for h in parity_heads}
     if world > 1:
         q_h, k_h, v_h = (x.chunk(world, dim=-2)[rank].contiguous() for x in (q_h, k_h, v_h))
     q_h, k_h, v_h = q_h.pin_memory(), k_h.pin_memory(), v_h.pin_memory()
     q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
 
+    if args.impl == "reference_gpu":
+        return run_reference_gpu(args, dict(torch=torch, dist=dist, world=world, rank=rank, dev=dev, mesh=mesh, U=U, R=R,
+                                            H=H, S_pad=S_pad, q=q, k=k, v=v, flush=flush, sampler=sampler,
+                                            causal=causal))
     if world == 1:
         def step(qq, kk, vv):
             return ops.attention_forward(qq, kk, vv, is_causal=causal)
-        launches_per_step = 1
+        launches_per_step = 1  # the attention kernel
     else:
         mode = pa.UnifiedAttnMode(mesh)
 
         def step(qq, kk, vv):
             with mode:
                 return torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=causal)
-        launches_per_step = 2 + (1 if U > 1 else 0)  # push + attention (+ output-arrival wait)
+        # the attention kernel (the exchange rides inside it); Ulysses meshes add the one-warp
+        # wait for the output tiles and the hand-out copy; causal runs one more one-warp wait
+        launches_per_step = 1 + (2 if U > 1 else 0) + (1 if causal else 0)
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -330,6 +368,37 @@ def run_ours(args):
     total_ms = timed(lambda: step(q, k, v), max(args.warmup, 3), args.steps, window)
     clocks = sampler.stop(window.get("begin"), window.get("end")) if rank == 0 else None
     pa.check_device_status()
+
+    # parity, outside the timed region: sampled output rows of this rank against the oracle
+    parity = None
+    if not args.no_parity and not causal:
+        import numpy as np
+
+        from oracle import cp_attention_oracle as O
+
+        out = step(q, k, v)
+        torch.cuda.synchronize(dev)
+        s_loc = q.shape[2]
+        rows = torch.randperm(s_loc, generator=torch.Generator().manual_seed(rank))[:512].sort().values
+        max_abs, num, den = 0.0, 0.0, 0.0
+        for h in parity_heads:
+            got = out[0, h, rows.to(dev)].float().cpu().numpy()
+            kf, vf = kv_full[h]
+            ref, _ = O.sdpa_with_lse(q[0, h, rows.to(dev)].float().cpu().numpy()[None, None], kf[None, None], vf[None, None])
+            ref = ref[0, 0]
+            max_abs = max(max_abs, float(np.abs(got - ref).max()))
+            num += float(((got - ref) ** 2).sum())
+            den += float((ref ** 2).sum())
+        stats = torch.tensor([max_abs, num, den], dtype=torch.float64, device=dev)
+        if world > 1:
+            mx = stats[:1].clone()
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            dist.all_reduce(stats, op=dist.ReduceOp.SUM)
+            stats[0] = mx[0]
+        max_abs, rel_l2 = float(stats[0]), math.sqrt(float(stats[1]) / max(float(stats[2]), 1e-30))
+        parity = {"rows": 512 * len(parity_heads) * world, "heads": parity_heads, "max_abs": max_abs, "rel_l2": rel_l2,
+                  "tolerance": {"max_abs": 2e-2, "rel_l2": 5e-3}, "ok": bool(max_abs <= 2e-2 and rel_l2 <= 5e-3),
+                  "against": "fp32 numpy oracle over all keys, real peers" if world > 1 else "fp32 numpy oracle over all keys"}
 
     flops = attention_flops(H, S_pad)
     ms_per_step = total_ms / args.steps
@@ -369,21 +438,23 @@ def run_ours(args):
                     "peak_source": f"{peaks['source']} cuBLAS bf16 burst", "kernel": "attn_fwd_kernel",
                     "flops_per_launch": flops}
     else:
-        # slower of tensor time and NVLink time (770 GB/s measured per direction per GPU)
+        # slower of tensor time and NVLink time at the nominal 900 GB/s per direction per GPU
         hl = H // U
         s_loc = S_pad // world
         sent = ((world - 1) * 2 + (U - 1) * 2) * hl * s_loc * VARIANT["D"] * 2  # K,V to all; Q out + O back
         t_tc = flops / world / (peaks["bf16_tflops"] * 1e12)
-        t_nv = sent / 770e9
+        t_nv = sent / NVLINK_GBS / 1e9
         roof = max(t_tc, t_nv)
         roofline = {"bound": "tensor" if t_tc >= t_nv else "nvlink", "achieved": per_gpu_tflops,
                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": roof / (ms_per_step * 1e-3),
-                    "traffic": None, "peak_source": f"{peaks['source']} cuBLAS bf16 burst; NVLink 770 GB/s measured",
-                    "exchanged_bytes_per_gpu": int(sent), "t_tensor_ms": t_tc * 1e3, "t_nvlink_ms": t_nv * 1e3}
+                    "traffic": None,
+                    "peak_source": f"{peaks['source']} cuBLAS bf16 burst; NVLink {NVLINK_GBS:.0f} GB/s per direction (nominal)",
+                    "exchanged_bytes_per_gpu": int(sent), "t_tensor_ms": t_tc * 1e3, "t_nvlink_ms": t_nv * 1e3,
+                    "nvlink_gbs_if_not_overlapped": sent / (ms_per_step * 1e-3) / 1e9}
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline and not causal and VARIANT["D"] == 128:
-        cv, sample = cpu_sample(H, S, budget_s=12.0)
-        cpu_baseline = {"value": cv, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port", "sample": sample}
+        cv, sample, kind = cpu_sample(H, S, budget_s=12.0, ref_dir=args.ref)
+        cpu_baseline = {"value": cv, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind, "sample": sample}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -391,26 +462,177 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": workload_name(H, S), "mesh": f"{U}x{R} (ulysses x ring)", "per_gpu_tflops": per_gpu_tflops,
                    "l2": "256 MB flush between timed iterations", "timing": "CUDA events per step, max over ranks"},
-        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "parity": parity,
         "gpu_launches": launches_per_step * args.steps,
     }
+    if world == 1 and roofline.get("traffic") is not None and (H, S) != (24, 8192):
+        roofline["traffic_scaled_from"] = "ncu capture at H=24 S=8192, scaled by S and heads"
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch. Captured with ncu
-# at H=24, S=8192 (profiles/attn_fwd_kernel_h24_s8192_ncu_full.md: 151.3 MB read + 33.6 MB
-# written = the q, k, v, out bytes); q, k, v and out grow linearly with S while the K/V of one
-# head (16.8 MB at S=32760) still fit the 126 MB L2, so the S=32760 rows are that capture
-# scaled by 32760/8192 (and by heads).
+NVLINK_GBS = 900.0  # per direction per GPU, NVLink 5 nominal
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_fwd_kernel launch, captured with ncu
+# at H=24, S=8192: 151.3 MB read + 33.6 MB written = the q, k, v, out bytes. q, k, v and out
+# grow linearly with S while the K/V of one head (16.8 MB at S=32760) still fit the 126 MB L2,
+# so the S=32760 rows are that capture scaled by 32760/8192 (and by heads).
 _CAPTURED = 184.93e6
 TRAFFIC_BYTES_PER_LAUNCH = {
     (24, 8192): _CAPTURED,
     (24, 32760): _CAPTURED * 32760 / 8192,
     (40, 32760): _CAPTURED * 32760 / 8192 * 40 / 24,
 }
+
+
+# ------------------------------------------------------------------------------------------
+# comparator: the reference's GPU path (library SDPA + NCCL) on the same GPUs
+# ------------------------------------------------------------------------------------------
+def run_reference_gpu(args, c):
+    """Times what the reference runs on GPUs for this step: at world size 1 PyTorch's SDPA; on a
+    mesh the Ulysses all-to-alls (src/para_attn/para_attn_interface.py:52-119) around PyTorch's
+    ring-attention loop (:162-239; torch/distributed/tensor/experimental/_context_parallel/
+    _attention.py) with the library SDPA kernel as its block op (src/para_attn/ops/__init__.py:48-110).
+    The flash and cuDNN backends are timed separately; ``value`` is the faster one."""
+    torch, dist = c["torch"], c["dist"]
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    world, rank, dev, mesh, U, R, H, S_pad = (c[k] for k in ("world", "rank", "dev", "mesh", "U", "R", "H", "S_pad"))
+    q, k, v, flush, causal = c["q"], c["k"], c["v"], c["flush"], c["causal"]
+    aten = torch.ops.aten
+
+    ref_pkg = None
+    for cand in ([args.ref] if args.ref else []) + [str(ROOT / "baseline" / "_ref")]:
+        if cand and (Path(cand) / "para_attn" / "__init__.py").exists():
+            sys.path.insert(0, str(cand))
+            import para_attn as ref_pkg  # noqa: F811
+            break
+
+    def block_op(backend):
+        """(out, lse) from the library kernel of one backend, as the reference's custom op returns it."""
+        def flash(qq, kk, vv, is_causal=False, dropout_p=0.0, scale=None, **_):
+            return aten._scaled_dot_product_flash_attention(qq, kk, vv, dropout_p=dropout_p, is_causal=is_causal,
+                                                            scale=scale)[:2]
+
+        def cudnn(qq, kk, vv, is_causal=False, dropout_p=0.0, scale=None, **_):
+            return aten._scaled_dot_product_cudnn_attention(qq, kk, vv, attn_bias=None, compute_log_sumexp=True,
+                                                            dropout_p=dropout_p, is_causal=is_causal, scale=scale)[:2]
+        return flash if backend == "flash" else cudnn
+
+    def a2a(x, pg):
+        import torch.distributed._functional_collectives as funcol
+
+        y = funcol.all_to_all_single(x.flatten(), None, None, pg)
+        y = y.wait() if isinstance(y, funcol.AsyncCollectiveTensor) else y
+        return y.reshape(x.shape)
+
+    def ulysses(qq, kk, vv, pg, inner):
+        n = dist.get_world_size(pg)
+
+        def seq_to_heads(x):  # [b, h, s, d] -> [b, h/n, n*s, d]
+            b, h, s, d = x.shape
+            x = a2a(x.permute(1, 0, 2, 3).contiguous(), pg)
+            return x.reshape(n, h // n, b, s, d).permute(2, 1, 0, 3, 4).reshape(b, h // n, n * s, d)
+
+        def heads_to_seq(x):  # [b, h/n, n*s, d] -> [b, h, s, d]
+            b, hl, s_all, d = x.shape
+            x = a2a(x.permute(2, 0, 1, 3).contiguous(), pg)
+            return x.reshape(n, s_all // n, b, hl, d).permute(2, 0, 3, 1, 4).reshape(b, n * hl, s_all // n, d)
+
+        return heads_to_seq(inner(seq_to_heads(qq), seq_to_heads(kk), seq_to_heads(vv)))
+
+    def ring(qq, kk, vv, pg, backend):
+        from torch.distributed.tensor.experimental._context_parallel import _attention as A
+
+        opts = A._cp_options
+        old = (opts.convert_to_f32, opts.enable_load_balance, opts.rotate_method)
+        opts.convert_to_f32, opts.enable_load_balance, opts.rotate_method = True, False, A._RotateMethod.ALL_TO_ALL
+        try:
+            out = A._templated_ring_attention(pg, 2, block_op(backend), qq, kk, vv, is_causal=causal, dropout_p=0.0,
+                                              scale=None)[0]
+        finally:
+            opts.convert_to_f32, opts.enable_load_balance, opts.rotate_method = old
+        return out.to(qq.dtype)
+
+    def make_step(backend):
+        sd = SDPBackend.FLASH_ATTENTION if backend == "flash" else SDPBackend.CUDNN_ATTENTION
+        if ref_pkg is not None:
+            mode = ref_pkg.UnifiedAttnMode(mesh) if world > 1 else None
+
+            def step():
+                with sdpa_kernel([sd]):
+                    if mode is None:
+                        return F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+                    with mode:
+                        return F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+            return step
+        ring_pg = mesh["ring"].get_group() if world > 1 else None
+        uly_pg = mesh["ulysses"].get_group() if world > 1 else None
+
+        def local(qq, kk, vv):
+            with sdpa_kernel([sd]):
+                return F.scaled_dot_product_attention(qq, kk, vv, is_causal=causal)
+
+        def inner(qq, kk, vv):
+            return ring(qq, kk, vv, ring_pg, backend) if R > 1 else local(qq, kk, vv)
+
+        def step():
+            return ulysses(q, k, v, uly_pg, inner) if U > 1 else inner(q, k, v)
+        return step
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    flops = attention_flops(H, S_pad)
+    backends, errors = {}, {}
+    for backend in ("flash", "cudnn"):
+        try:
+            fn = make_step(backend)
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            sync_all()
+            evs = []
+            for _ in range(args.steps):
+                flush.fill_(1)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                evs.append((e0, e1))
+            sync_all()
+            t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            backends[backend] = flops / (float(t.item()) / args.steps * 1e-3) / 1e12
+        except Exception as e:  # a backend the library refuses for this shape
+            errors[backend] = f"{type(e).__name__}: {str(e)[:160]}"
+    c["sampler"].stop()
+    if rank == 0:
+        if backends:
+            best = max(backends, key=backends.get)
+            value = backends[best]
+            line = {"impl": "reference_gpu", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+                    "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": flops / value / 1e9,
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                    "config": {"workload": workload_name(H, c["S_pad"]), "mesh": f"{U}x{R} (ulysses x ring)",
+                               "per_gpu_tflops": value / world, "l2": "256 MB flush between timed iterations",
+                               "timing": "CUDA events per step, max over ranks"},
+                    "backends_tflops": backends, "backend_errors": errors, "best_backend": best,
+                    "kind": "reference package" if ref_pkg is not None else
+                            "the reference's sequence of library calls (torch SDPA, NCCL all_to_all, torch ring loop) issued from bench.py",
+                    "gpu_launches": 0}
+        else:
+            line = {"impl": "reference_gpu", "unavailable": "; ".join(f"{b}: {e}" for b, e in errors.items())[:300]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 # ------------------------------------------------------------------------------------------
@@ -582,6 +804,8 @@ if __name__ == "__main__":
     VARIANT["D"], VARIANT["causal"] = a.head_dim, a.causal
     if a.impl == "reference":
         run_reference(a)
+    elif a.impl == "reference_gpu" and a.workload != "attention":
+        print(json.dumps({"impl": "reference_gpu", "unavailable": "the comparator covers the attention workload only"}))
     elif a.workload == "fbcache":
         run_fbcache_kernels(a)
     elif a.workload != "attention":

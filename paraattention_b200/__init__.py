@@ -27,7 +27,7 @@ from .para_attn_interface import (  # noqa: E402
     UlyssesAttnMode,
     UnifiedAttnMode,
 )
-from ._cp_engine import check_device_status  # noqa: E402
+from ._cp_engine import check_device_status, reset_device_status  # noqa: E402
 from .host_io import attention_from_host  # noqa: E402
 
 __all__ = [
@@ -41,6 +41,7 @@ __all__ = [
     "ulysses_attn_func",
     "in_batch_attn_func",
     "check_device_status",
+    "reset_device_status",
     "attention_from_host",
     "install_as_para_attn",
 ]

@@ -28,9 +28,21 @@ import torch
 import torch.distributed as dist
 
 from . import _lib as L
+from . import _status
 from . import config
 
 _ALIGN = 1024
+
+
+_SM_COUNTS: Dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    n = _SM_COUNTS.get(device.index)
+    if n is None:
+        n = torch.cuda.get_device_properties(device).multi_processor_count
+        _SM_COUNTS[device.index] = n
+    return n
 
 
 def _round_up(x: int, a: int) -> int:
@@ -329,6 +341,7 @@ class CpEngine:
         self.device = device
         self.capacity = (0, 0, 0)  # kv_chunk_bytes, q_chunk_bytes, out_bytes
         self.ws: Optional[Workspace] = None
+        self.status: Optional[_status.StatusMirror] = None
         self.hdl = None
         self.state = CallState()
         self._launch_cache: Dict[Tuple, Tuple] = {}
@@ -362,15 +375,29 @@ class CpEngine:
         self.capacity, self.hdl = cap, hdl
         self.ws = Workspace(layout, buf, peer, self.r * self.ulysses + self.u)
         self.state = CallState()
+        self.status = _status.StatusMirror(self.ws.status_tensor())
         self._launch_cache.clear()
 
     def check_status(self) -> None:
-        """Host-synchronising check of the device status word (tests and debugging)."""
+        """Host-synchronising check of the device status word."""
+        if self.status is not None:
+            self.status.check_now()
+
+    def reset(self) -> None:
+        """Recover after a timed-out wait: collective over the group. Clears the status word and
+        the exchange counters on every rank and restarts the call count, so that the expected
+        counter values agree again whatever each rank managed to do in the failed call."""
         if self.ws is None:
             return
-        st = int(self.ws.status_tensor().item())
-        if st != 0:
-            raise L.PaError(L.PA_ETIMEDOUT, L.DEV_STATUS_NAMES.get(st, f"device status {st}"))
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # nobody is still adding to anybody's counters
+        lay = self.ws.layout
+        self.ws.buf[lay.stage_bytes:lay.total].zero_()  # arrival and output counters, status word
+        self.state = CallState()
+        self._launch_cache.clear()
+        self.status.reset()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
 
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float],
                   is_causal: bool = False, key_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -381,6 +408,8 @@ class CpEngine:
         skv = k.shape[2]
         plan = CpPlan(self.ulysses, self.ring, self.u, self.r, H)
         self._ensure(stage_sizes(plan, B, sq, skv, D, q.element_size()))
+        # a wait that ran out in an earlier call is raised here, from host memory (no device sync)
+        self.status.check()
         ws, st = self.ws, self.state
         par = st.calls & 1
         st.calls += 1
@@ -394,7 +423,7 @@ class CpEngine:
             ctas = (sent + (5 << 20) - 1) // (5 << 20)
             # SMs that the last, partly filled wave of the grid leaves idle can push for free
             grid = ((sq + 255) // 256) * hl * B * self.ulysses
-            spare = (-grid) % 148
+            spare = (-grid) % _sm_count(self.device)
             ctas = max(16, min(64, max(ctas, min(spare, 48))))
         wait_ns = config.cp.wait_limit_ns
         scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
@@ -451,6 +480,7 @@ class CpEngine:
             L.check(L.load().pa_flag_wait(flags, len(others), st.arrive_expect[par], ws.base + lay.off_status,
                                           wait_ns, 3, main.cuda_stream))
         if out_local is not None:
+            self.status.refresh()
             return out_local
 
         # 3. wait for the tiles owed to me, then hand out a private copy
@@ -459,6 +489,10 @@ class CpEngine:
         lay = ws.layout
         out_bytes = B * sq * H * D * q.element_size()
         o_stage = ws.buf[lay.off_o[par]:lay.off_o[par] + out_bytes].view(q.dtype).view(B, sq, H, D)
+        self.status.refresh()
+        if config.cp.zero_copy_output:
+            # the staging view itself: valid until the second-next call of this engine reuses the parity
+            return o_stage.transpose(1, 2)
         return o_stage.clone().transpose(1, 2)
 
 
@@ -495,6 +529,17 @@ def engine_by_id(i: int) -> CpEngine:
 
 
 def check_device_status() -> None:
-    """Raise if any context-parallel kernel reported a timed-out wait (synchronises)."""
+    """Raise if any attention kernel of this process reported a timed-out wait (synchronises)."""
     for eng in _engines.values():
         eng.check_status()
+    for mirror in _status.all_mirrors():
+        mirror.check_now()
+
+
+def reset_device_status() -> None:
+    """Clear every status word and resynchronise the exchange counters (collective over each
+    engine's group): the way back to a usable state after a ``PaError(PA_ETIMEDOUT)``."""
+    for eng in _engines.values():
+        eng.reset()
+    for mirror in _status.all_mirrors():
+        mirror.reset()

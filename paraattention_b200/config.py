@@ -2,9 +2,12 @@
 
 ``attention.force_dispatch_to_custom_ops``: in the reference it routes the final,
 non-parallel SDPA of ``UnifiedAttnMode`` through the custom op instead of
-``F.scaled_dot_product_attention``. Here the custom op *is* the product path, so the CUDA
-bf16/f16 head_dim 64 / 128 case always goes to it; the flag additionally makes unsupported
-inputs raise instead of being handed back to PyTorch's own SDPA.
+``F.scaled_dot_product_attention``. Here the custom op *is* the product path; the flag is kept
+for code that sets it and changes nothing.
+
+``attention.allow_sdpa_fallback`` (no counterpart in the reference): an attention call inside a
+mode that the sm_100a kernel does not cover raises; with this set it goes to PyTorch's own
+SDPA instead. Off by default: nothing leaves the kernel path silently.
 
 ``attention.allow_reduced_precision_compute``: the reference lets torch's ring merger run in
 the block dtype when set. The fused kernel always accumulates and merges in fp32 on chip,
@@ -17,6 +20,7 @@ import sys
 class attention:
     force_dispatch_to_custom_ops = os.getenv("PARA_ATTN_FORCE_DISPATCH_TO_CUSTOM_OPS") == "1"
     allow_reduced_precision_compute = os.getenv("PARA_ATTN_ALLOW_REDUCED_PRECISION_COMPUTE") == "1"
+    allow_sdpa_fallback = os.getenv("PA_B200_ALLOW_SDPA_FALLBACK") == "1"
 
 
 class cp:
@@ -24,6 +28,10 @@ class cp:
 
     # how many leading CTAs of the attention grid do the exchange (0 = choose from the bytes to send)
     push_ctas_per_dest = int(os.getenv("PA_B200_PUSH_CTAS", "0"))
+    # Ulysses output: hand out the staging buffer itself instead of a private copy. The tensor is
+    # then overwritten by the second-next attention call of the same mesh: only for callers that
+    # consume an attention result before issuing two more (every transformer block does).
+    zero_copy_output = os.getenv("PA_B200_ZERO_COPY_OUTPUT") == "1"
     # device-side bound on every wait for a peer, in nanoseconds
     wait_limit_ns = int(os.getenv("PA_B200_WAIT_LIMIT_NS", str(5_000_000_000)))
 

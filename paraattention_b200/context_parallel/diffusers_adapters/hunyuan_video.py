@@ -10,12 +10,21 @@ The reference builds a key-padding mask over video + text tokens, re-orders it t
 interleaved layout (:74-100) and lets ``SparseKVAttnMode`` drop padded keys before attention
 (:112). Here the mask - in the same interleaved order, one [video shard, text shard] piece per
 rank of the sequence mesh - goes into the chunked attention kernel, which also works when the
-mesh has a ring dimension. A prompt mask without padding is dropped, which is exact.
+mesh has a ring dimension. The mask is always passed (an all-true mask costs the kernel nothing
+worth a device-to-host round trip to find out), so a forward has no host synchronisation.
+PEFT LoRA scaling (``attention_kwargs["scale"]``, :54-67 and :124-126 of the reference) is applied
+when diffusers is importable.
 """
 import functools
 from typing import Any, Dict, Optional, Union
 
 import torch
+
+try:  # LoRA scale handling needs diffusers; the duck-typed stand-ins of this package do not
+    from diffusers.utils import scale_lora_layers, unscale_lora_layers, USE_PEFT_BACKEND
+except Exception:  # pragma: no cover - diffusers is optional
+    scale_lora_layers = unscale_lora_layers = None
+    USE_PEFT_BACKEND = False
 
 from ... import primitives as DP
 from ...para_attn_interface import UnifiedAttnMode
@@ -42,6 +51,13 @@ def parallelize_transformer(transformer, *, mesh=None):
         return_dict: bool = True,
         **kwargs,
     ) -> Union[torch.Tensor, Dict[str, torch.Tensor]]:
+        lora_scale = 1.0
+        if attention_kwargs is not None:
+            attention_kwargs = dict(attention_kwargs)
+            lora_scale = attention_kwargs.pop("scale", 1.0)
+        if USE_PEFT_BACKEND and scale_lora_layers is not None:
+            scale_lora_layers(self, lora_scale)
+
         batch_size, num_channels, num_frames, height, width = hidden_states.shape
         p, p_t = self.config.patch_size, self.config.patch_size_t
         post_patch_num_frames = num_frames // p_t
@@ -54,18 +70,16 @@ def parallelize_transformer(transformer, *, mesh=None):
         hidden_states = self.x_embedder(hidden_states)
         encoder_hidden_states = self.context_embedder(encoder_hidden_states, timestep, encoder_attention_mask)
 
-        attention_mask = None  # every key is valid
         prompt_mask = encoder_attention_mask.to(torch.bool)
-        if not bool(prompt_mask.all()):
-            world = DP.get_world_size(seq_mesh)
-            n_video, n_text = hidden_states.shape[1], encoder_hidden_states.shape[1]
-            assert n_video % world == 0 and n_text % world == 0, "sequence lengths must divide by the mesh size"
-            video = torch.ones(batch_size, n_video // world, dtype=torch.bool, device=prompt_mask.device)
-            pieces = []
-            for piece in prompt_mask.chunk(world, dim=-1):
-                pieces += [video, piece]
-            attention_mask = torch.cat(pieces, dim=-1)[:, None, None, :]
-            attention_mask = DP.get_assigned_chunk(attention_mask, dim=0, group=batch_mesh)
+        world = DP.get_world_size(seq_mesh)
+        n_video, n_text = hidden_states.shape[1], encoder_hidden_states.shape[1]
+        assert n_video % world == 0 and n_text % world == 0, "sequence lengths must divide by the mesh size"
+        video = torch.ones(batch_size, n_video // world, dtype=torch.bool, device=prompt_mask.device)
+        pieces = []
+        for piece in prompt_mask.chunk(world, dim=-1):
+            pieces += [video, piece]
+        attention_mask = torch.cat(pieces, dim=-1)[:, None, None, :]
+        attention_mask = DP.get_assigned_chunk(attention_mask, dim=0, group=batch_mesh)
 
         temb = DP.get_assigned_chunk(temb, dim=0, group=batch_mesh)
         hidden_states = DP.get_assigned_chunk(hidden_states, dim=0, group=batch_mesh)
@@ -96,6 +110,8 @@ def parallelize_transformer(transformer, *, mesh=None):
         hidden_states = hidden_states.flatten(6, 7).flatten(4, 5).flatten(2, 3)
         if isinstance(timestep, torch.Tensor) and timestep.is_floating_point():
             hidden_states = hidden_states.to(timestep.dtype)
+        if USE_PEFT_BACKEND and unscale_lora_layers is not None:
+            unscale_lora_layers(self, lora_scale)
         return make_output(getattr(self, "output_class", None), hidden_states, return_dict)
 
     transformer.forward = new_forward.__get__(transformer)

@@ -206,6 +206,15 @@ def get_downsample_factor():
     return _ctx().downsample_factor
 
 
+# Like the reference's (utils.py:123-190), the accessors stay outside compiled regions: they
+# read and write Python state that a tracing compiler must not bake into a graph.
+for _name in ("get_residual_diff_threshold", "get_buffer", "set_buffer", "remove_buffer", "mark_step_begin",
+              "is_taylorseer_enabled", "get_taylorseer", "is_slg_enabled", "slg_should_skip_block", "is_in_warmup",
+              "get_downsample_factor"):
+    globals()[_name] = torch.compiler.disable(globals()[_name])
+del _name
+
+
 # --------------------------------------------------------------------------------------------
 # device work
 # --------------------------------------------------------------------------------------------
@@ -233,16 +242,18 @@ def _require_cuda(t: torch.Tensor):
         raise RuntimeError("First Block Cache kernels need CUDA tensors; there is no CPU path in this package")
 
 
-def fused_residual_diff(h1: torch.Tensor, h0: torch.Tensor, prev: Optional[torch.Tensor], *, downsample: int = 1,
-                        store: bool = True):
+@torch.compiler.disable
+def fused_residual_diff(h1: torch.Tensor, h0: Optional[torch.Tensor], prev: Optional[torch.Tensor], *,
+                        downsample: int = 1, store: bool = True):
     """One launch: ``cur = h1 - h0`` (rounded to the tensors' dtype, optionally only every
-    ``downsample``-th channel), and if ``prev`` is given the fp32 sums / rounded means / rounded
-    ratio of ``are_two_tensors_similar(prev, cur)`` (src/para_attn/first_block_cache/utils.py:228-233).
+    ``downsample``-th channel; ``h0 = None`` means ``cur = h1``), and if ``prev`` is given the fp32
+    sums / rounded means / rounded ratio of ``are_two_tensors_similar(prev, cur)``
+    (src/para_attn/first_block_cache/utils.py:228-233).
 
     Returns ``(cur or None, result)`` with ``result`` a 5-float device tensor
     [sum|prev-cur|, sum|prev|, mean_diff, mean_prev, mean_diff/mean_prev]."""
     _require_cuda(h1)
-    assert h1.shape == h0.shape and h1.dtype == h0.dtype
+    assert h0 is None or (h1.shape == h0.shape and h1.dtype == h0.dtype)
     if not _kernel_ok(h1, h0, prev):
         raise NotImplementedError("fused_residual_diff needs contiguous CUDA bf16/f16 tensors of one dtype")
     cols = h1.shape[-1]
@@ -254,23 +265,29 @@ def fused_residual_diff(h1: torch.Tensor, h0: torch.Tensor, prev: Optional[torch
     cur = torch.empty(new_shape, dtype=h1.dtype, device=h1.device) if store else None
     result = torch.empty(5, dtype=torch.float32, device=h1.device)
     L.check(L.load().pa_fbc_residual_diff(
-        h1.data_ptr(), h0.data_ptr(), prev.data_ptr() if prev is not None else None,
+        h1.data_ptr(), h0.data_ptr() if h0 is not None else None, prev.data_ptr() if prev is not None else None,
         cur.data_ptr() if cur is not None else None, rows, cols, downsample, _DTYPES[h1.dtype], result.data_ptr(),
         _scratch_for(h1.device).data_ptr(), torch.cuda.current_stream(h1.device).cuda_stream))
     return cur, result
 
 
+@torch.compiler.disable
 def _axpy(a: torch.Tensor, b: torch.Tensor, sub: bool) -> torch.Tensor:
+    """``a - b`` / ``a + b`` rounded to the tensors' 16-bit type: one launch of pa_fbc_axpy (any
+    size and 2-byte alignment; sizes that are not a multiple of 8 take its scalar form)."""
     _require_cuda(a)
-    if _kernel_ok(a, b) and a.shape == b.shape and a.numel() % 8 == 0 and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0:
-        out = torch.empty_like(a)
+    if not (_kernel_ok(a, b) and a.shape == b.shape):
+        raise NotImplementedError(
+            f"cached residual arithmetic needs two contiguous CUDA bf16/f16 tensors of one shape and dtype, got "
+            f"{a.dtype} {tuple(a.shape)} and {b.dtype} {tuple(b.shape)}")
+    out = torch.empty_like(a)
+    if a.numel() > 0:
         L.check(L.load().pa_fbc_axpy(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), 1 if sub else 0,
                                      _DTYPES[a.dtype], torch.cuda.current_stream(a.device).cuda_stream))
-        return out
-    # shapes the vector kernel does not take (odd sizes, fp32, broadcasting): same arithmetic in ATen
-    return (a - b if sub else a + b).contiguous()
+    return out
 
 
+@torch.compiler.disable
 def _decide(result: torch.Tensor, dtype: torch.dtype, threshold: float, parallelized: bool) -> bool:
     if parallelized:
         # the reference averages each rounded mean over the default group (utils.py:230-232)
@@ -282,6 +299,7 @@ def _decide(result: torch.Tensor, dtype: torch.dtype, threshold: float, parallel
     return diff.item() < threshold
 
 
+@torch.compiler.disable
 def are_two_tensors_similar(t1, t2, *, threshold, parallelized=False):
     """mean|t1 - t2| / mean|t1| < threshold with the reference's rounding (utils.py:220-234)."""
     if threshold <= 0.0:
@@ -289,11 +307,11 @@ def are_two_tensors_similar(t1, t2, *, threshold, parallelized=False):
     if t1.shape != t2.shape:
         return False
     _require_cuda(t1)
-    zero = torch.zeros_like(t2)
-    _, result = fused_residual_diff(t2.contiguous(), zero, t1.contiguous(), store=False)
+    _, result = fused_residual_diff(t2.contiguous(), None, t1.contiguous(), store=False)
     return _decide(result, t1.dtype, threshold, parallelized)
 
 
+@torch.compiler.disable
 def apply_prev_hidden_states_residual(hidden_states, encoder_hidden_states=None):
     if is_taylorseer_enabled():
         # extrapolated residual + hidden states in one launch; the encoder states pass through
@@ -320,6 +338,7 @@ def _every_nth_channel(residual: torch.Tensor, contiguous: bool = False) -> torc
     return view.contiguous() if contiguous else view
 
 
+@torch.compiler.disable
 def get_can_use_cache(first_hidden_states_residual, parallelized=False):
     """Reference-shaped entry (utils.py:269-286) for callers that already hold the residual:
     no reuse during warm-up, with a threshold of zero, or before a first residual exists."""
@@ -333,6 +352,7 @@ def get_can_use_cache(first_hidden_states_residual, parallelized=False):
                                    parallelized=parallelized)
 
 
+@torch.compiler.disable
 def set_first_hidden_states_residual(first_hidden_states_residual):
     set_buffer("first_hidden_states_residual", _every_nth_channel(first_hidden_states_residual, contiguous=True))
 
@@ -341,6 +361,7 @@ def get_first_hidden_states_residual():
     return get_buffer("first_hidden_states_residual")
 
 
+@torch.compiler.disable
 def set_hidden_states_residual(hidden_states_residual):
     """Keep the residual of the skipped blocks: as a buffer, or as a new sample of the extrapolator."""
     if is_taylorseer_enabled():
@@ -349,6 +370,7 @@ def set_hidden_states_residual(hidden_states_residual):
     set_buffer("hidden_states_residual", hidden_states_residual)
 
 
+@torch.compiler.disable
 def get_hidden_states_residual():
     if is_taylorseer_enabled():
         return get_taylorseer().approximate_value()
@@ -365,6 +387,7 @@ def get_encoder_hidden_states_residual():
     return get_buffer("encoder_hidden_states_residual")
 
 
+@torch.compiler.disable
 def first_block_decision(hidden_states, original_hidden_states, parallelized=False) -> bool:
     """Fused form of utils.py:359-381: residual of the first block, comparison with the previous
     step's, and - on a miss - storing it as the new reference. Returns can_use_cache."""

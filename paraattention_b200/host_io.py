@@ -21,16 +21,15 @@ from . import ops as para_attn_ops
 
 __all__ = ["attention_from_host", "HostAttentionPipeline"]
 
-_SM_COUNT = 148
 
 
-def _default_groups(heads: int, rows: int, batch: int, multiple_of: int, shard: int) -> int:
+def _default_groups(heads: int, rows: int, batch: int, multiple_of: int, shard: int, sm_count: int = 148) -> int:
     """How many groups of heads a call is split into; heads per group stay a multiple of
     ``multiple_of`` (the Ulysses size). A CTA covers 256 query rows of one head.
 
     One GPU: launches of neighbouring groups overlap (two compute streams), so up to 12 groups
     as long as a launch still has 1.5 waves of CTAs. Context parallel: the calls of one rank run
-    one after the other and each costs whole rounds of the 148 SMs, so at most 4 groups, and only
+    one after the other and each costs whole rounds of the SMs (148 on a B200), so at most 4 groups, and only
     if splitting adds no more than a tenth to the number of rounds (24 heads on 8 ranks: three
     calls of 128 CTAs are exactly the three rounds of one call of 384)."""
     pairs = (rows + 255) // 256
@@ -40,14 +39,14 @@ def _default_groups(heads: int, rows: int, batch: int, multiple_of: int, shard: 
 
     single_gpu = multiple_of * shard == 1
     best = 1
-    rounds_1 = -(-ctas(1) // _SM_COUNT)
+    rounds_1 = -(-ctas(1) // sm_count)
     for g in range(2, (12 if single_gpu else 4) + 1):
         if heads % g or (heads // g) % multiple_of:
             continue
         if single_gpu:
-            ok = ctas(g) >= (3 * _SM_COUNT) // 2
+            ok = ctas(g) >= (3 * sm_count) // 2
         else:
-            ok = g * -(-ctas(g) // _SM_COUNT) <= 1.1 * rounds_1
+            ok = g * -(-ctas(g) // sm_count) <= 1.1 * rounds_1
         if ok:
             best = g
     return best
@@ -142,7 +141,8 @@ def attention_from_host(query: torch.Tensor, key: torch.Tensor, value: torch.Ten
     if out is None:
         out = torch.empty(query.shape, dtype=query.dtype).pin_memory()
     if head_groups is None:
-        head_groups = _default_groups(H, Sq, B, U, U)
+        head_groups = _default_groups(H, Sq, B, U, U,
+                                      torch.cuda.get_device_properties(device).multi_processor_count)
     assert H % head_groups == 0 and (H // head_groups) % U == 0, "head_groups must split the heads evenly per rank"
     # a causal mask couples nothing across heads either, so the same grouping applies
     if U * R > 1:

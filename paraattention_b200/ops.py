@@ -16,6 +16,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib as L
+from . import _status
 
 __all__ = [
     "attention_forward_with_lse",
@@ -72,15 +73,32 @@ def key_mask_of(attn_mask: Optional[torch.Tensor], batch: int, keys: int) -> Opt
     return m[:, 0, 0, :].expand(batch, keys)
 
 
+# Packed words of the last few masks. A diffusion transformer hands the same mask tensor to every
+# attention of a forward (60 calls for a HunyuanVideo-shaped model): it is packed once. An entry
+# keeps its mask tensor alive, so "same storage address, same version counter, same layout" can
+# only mean the same contents.
+_PACK_CACHE: list = []
+_PACK_CACHE_SIZE = 4
+
+
 def pack_key_mask(key_mask: torch.Tensor, n_chunks: int, rows: int) -> torch.Tensor:
     """pa_pack_key_mask: [batch, n_chunks * rows] bool -> [batch, n_chunks, ceil(rows / 64)] words
     (int64 storage) as the attention entry points read them."""
     assert key_mask.dtype == torch.bool and key_mask.ndim == 2 and key_mask.shape[1] == n_chunks * rows
     assert key_mask.device.type == "cuda", "Must be CUDA tensors"
+    ident = (key_mask.data_ptr(), key_mask._version, tuple(key_mask.shape), key_mask.stride(), n_chunks, rows,
+             key_mask.device.index)
+    for i, (k, _, words) in enumerate(_PACK_CACHE):
+        if k == ident:
+            if i:
+                _PACK_CACHE.insert(0, _PACK_CACHE.pop(i))
+            return words
     m = key_mask.contiguous()
     out = torch.empty((m.shape[0], n_chunks, (rows + 63) // 64), dtype=torch.int64, device=m.device)
     L.check(L.load().pa_pack_key_mask(m.data_ptr(), m.stride(0), m.shape[0], n_chunks, rows, out.data_ptr(),
                                       torch.cuda.current_stream(m.device).cuda_stream))
+    _PACK_CACHE.insert(0, (ident, key_mask, out))
+    del _PACK_CACHE[_PACK_CACHE_SIZE:]
     return out
 
 
@@ -104,11 +122,20 @@ def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: b
     a.scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
     for i in range(3):
         a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
-    a.status = status.data_ptr() if status is not None else None
+    # Without a status word of the caller's, the process-wide one of this device: a wait that ran
+    # out in an earlier launch is raised here, and this launch's outcome is queued for the next.
+    mirror = None
+    if status is None:
+        mirror = _status.single_gpu_status(query.device)
+        mirror.check()
+        status = mirror.word
+    a.status = status.data_ptr()
     a.wait_limit_ns = 0
     bits = pack_key_mask(key_mask, 1, Skv) if key_mask is not None else None
     a.key_bits = bits.data_ptr() if bits is not None else None
     L.check(L.load().pa_attn_fwd(C.byref(a), torch.cuda.current_stream(query.device).cuda_stream))
+    if mirror is not None:
+        mirror.refresh()
     return out, lse
 
 

@@ -19,7 +19,7 @@ import torch.nn.functional as F
 from . import _cp_engine
 from . import ops as para_attn_ops
 from . import primitives as DP
-from .utils import base_handle_torch_function, BaseTorchFunctionMode, get_force_dispatch_to_custom_ops
+from .utils import base_handle_torch_function, BaseTorchFunctionMode, get_allow_sdpa_fallback
 
 __all__ = [
     "UnifiedAttnMode",
@@ -59,16 +59,21 @@ def _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal, total_ke
 
 def _local_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False, *, scale=None):
     """The non-parallel SDPA at the bottom of every mode (state "none" of the reference,
-    src/para_attn/para_attn_interface.py:468-475)."""
+    src/para_attn/para_attn_interface.py:468-475): the sm_100a kernel. A call the kernel does
+    not cover (CPU tensors, fp32, another head_dim, a general mask, dropout) raises; only with
+    ``config.attention.allow_sdpa_fallback`` set is it handed to PyTorch's own SDPA instead."""
     if _kernel_can_run(query, key, value, attn_mask, dropout_p, is_causal):
         if attn_mask is not None:
             return para_attn_ops.attention_forward_sparse_kv(query, key, value, attn_mask=attn_mask, scale=scale)
         return para_attn_ops.attention_forward(query, key, value, is_causal=is_causal, scale=scale)
-    if get_force_dispatch_to_custom_ops():
-        return para_attn_ops.attention_forward(
+    if get_allow_sdpa_fallback():
+        return F.scaled_dot_product_attention(
             query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale)
-    return F.scaled_dot_product_attention(
-        query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal, scale=scale)
+    raise NotImplementedError(
+        "attention outside the sm_100a kernel's coverage (CUDA bf16/f16, head_dim 64 or 128, no dropout, no mask other "
+        f"than a boolean key-padding mask): got {query.device.type} {query.dtype} head_dim {query.shape[-1]}"
+        f"{', a mask' if attn_mask is not None else ''}{', dropout' if dropout_p else ''}. "
+        "Set paraattention_b200.config.attention.allow_sdpa_fallback = True to let PyTorch's SDPA take such calls.")
 
 
 @torch.compiler.assume_constant_result
@@ -203,24 +208,21 @@ def in_batch_attn_func(
     *,
     scale=None,
 ):
-    assert query.ndim == 4, "query must have 4 dimensions, got {}".format(query.ndim)
-    assert key.ndim == 4, "key must have 4 dimensions, got {}".format(key.ndim)
-    assert value.ndim == 4, "value must have 4 dimensions, got {}".format(value.ndim)
+    """Every batch element attends to the keys of ALL batch elements
+    (src/para_attn/para_attn_interface.py:242-276): the batch is folded into the sequence, one
+    attention runs over [1, H, B*S, D], and the result is unfolded again."""
+    for name, t in (("query", query), ("key", key), ("value", value)):
+        assert t.ndim == 4, "{} must have 4 dimensions, got {}".format(name, t.ndim)
     assert attn_mask is None, "attn_mask is not supported in in_batch_attn_func"
     assert not is_causal, "is_causal is not supported in in_batch_attn_func"
 
-    b, h, s_q, d_qk = query.shape
-    _, _, s_kv, d_v = value.shape
+    batch, heads, s_q = query.shape[:3]
 
-    query = query.permute(1, 0, 2, 3).reshape(1, h, b * s_q, -1)
-    key = key.permute(1, 0, 2, 3).reshape(1, h, b * s_kv, -1)
-    value = value.permute(1, 0, 2, 3).reshape(1, h, b * s_kv, -1)
+    def fold(t):  # [B, H, S, D] -> [1, H, B*S, D]
+        return t.transpose(0, 1).reshape(1, heads, batch * t.shape[2], t.shape[3])
 
-    out = _local_attention(query, key, value, attn_mask=attn_mask, dropout_p=dropout_p, is_causal=is_causal,
-                           scale=scale)
-
-    out = out.reshape(h, b, s_q, -1).permute(1, 0, 2, 3)
-    return out
+    folded = _local_attention(fold(query), fold(key), fold(value), dropout_p=dropout_p, scale=scale)
+    return folded.reshape(heads, batch, s_q, folded.shape[-1]).transpose(0, 1)
 
 
 def _get_arg(args, kwargs, *field):
@@ -356,8 +358,12 @@ class UnifiedAttnMode(_AttnModeBase):
         is_causal = False if is_causal is None else is_causal
         U = DP.get_world_size(self._ulysses_mesh) if self._ulysses_mesh is not None else 1
         R = DP.get_world_size(self._ring_mesh) if self._ring_mesh is not None else 1
-        if U * R <= 1 and self._attn_func is not None:
-            return self._attn_func(*args, **kwargs)
+        if self._attn_func is not None and self._attn_func is not F.scaled_dot_product_attention:
+            if U * R <= 1:
+                return self._attn_func(*args, **kwargs)
+            raise NotImplementedError(
+                "UnifiedAttnMode with a custom attn_func on a parallel mesh: the exchange is fused into the attention "
+                "kernel and cannot wrap a foreign attention function")
         return unified_attn_func(query, key, value, attn_mask, dropout_p, is_causal, scale=scale,
                                  ulysses_mesh=self._ulysses_mesh, ring_mesh=self._ring_mesh,
                                  flat_group=self._flat_group)

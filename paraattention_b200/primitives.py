@@ -61,7 +61,15 @@ def all_to_all_single_sync(x, *args, **kwargs):
 
 
 def all_reduce_sync(x, *args, group=None, **kwargs):
-    return _finished(funcol.all_reduce(x, *args, group=get_group(group), **kwargs))
+    """``funcol.all_reduce`` that returns a finished tensor (src/para_attn/primitives.py:90-94).
+    The gloo backend has no "avg" reduction: there the average is the fp32 sum divided by the
+    group size and rounded back to the tensor's dtype (NCCL groups use NCCL's own "avg")."""
+    pg = get_group(group)
+    op = args[0] if args else kwargs.get("reduceOp")
+    if isinstance(op, str) and op.lower() == "avg" and dist.get_backend(pg) == "gloo":
+        total = _finished(funcol.all_reduce(x.float(), "sum", group=pg))
+        return (total / dist.get_world_size(pg)).to(x.dtype)
+    return _finished(funcol.all_reduce(x, *args, group=pg, **kwargs))
 
 
 # ------------------------------------------------------------------------------------------

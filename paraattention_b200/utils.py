@@ -18,6 +18,11 @@ def get_force_dispatch_to_custom_ops() -> bool:
     return bool(config.attention.force_dispatch_to_custom_ops)
 
 
+@torch.compiler.assume_constant_result
+def get_allow_sdpa_fallback() -> bool:
+    return bool(config.attention.allow_sdpa_fallback)
+
+
 class BaseTorchFunctionMode(TorchFunctionMode):
     """TorchFunctionMode whose construction stays outside compiled regions."""
 

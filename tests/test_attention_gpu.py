@@ -321,3 +321,38 @@ def test_full_size_properties():
     assert rc == 0
     assert (out2.float() - out.float()).abs().max().item() <= 2e-2
     assert (lse2 - lse).abs().max().item() <= 1e-3
+
+
+def test_sticky_device_status_is_raised_and_can_be_reset():
+    """A status word that an earlier launch left non-zero makes every later launch return at its
+    entry; the ops must say so instead of handing out garbage, and reset_device_status() recovers."""
+    import paraattention_b200 as pa
+    from paraattention_b200 import _lib as L
+    from paraattention_b200 import _status
+
+    q, k, v = seeded_qkv(1, 2, 256, 256, seed=5)
+    good = torch.ops.para_attn.attention_forward(q, k, v)
+    mirror = _status.single_gpu_status(q.device)
+    mirror.word.fill_(L.PA_DEV_TIMEOUT_PIPE)  # what a wait that ran out would have written
+    torch.ops.para_attn.attention_forward(q, k, v)  # this launch drains at once and queues the status copy
+    torch.cuda.synchronize()
+    with pytest.raises(L.PaError) as e:
+        torch.ops.para_attn.attention_forward(q, k, v)
+    assert e.value.code == L.PA_ETIMEDOUT
+    with pytest.raises(L.PaError):
+        pa.check_device_status()
+    pa.reset_device_status()
+    pa.check_device_status()
+    assert torch.equal(torch.ops.para_attn.attention_forward(q, k, v), good)
+
+
+def test_packed_key_mask_is_reused_until_the_mask_changes():
+    from paraattention_b200 import ops
+
+    m = torch.rand(2, 200, generator=torch.Generator().manual_seed(9)).cuda() < 0.5
+    w1 = ops.pack_key_mask(m, 1, 200)
+    assert ops.pack_key_mask(m, 1, 200) is w1            # same tensor, same version: packed once
+    before = w1.clone()
+    m[0, 3] = ~m[0, 3]                                   # an in-place change bumps the version counter
+    w2 = ops.pack_key_mask(m, 1, 200)
+    assert w2 is not w1 and not torch.equal(w2, before)

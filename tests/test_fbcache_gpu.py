@@ -195,3 +195,41 @@ def test_taylorseer_fused_add_and_refusals():
         seer.update(torch.zeros(3, 5, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(NotImplementedError):
         seer.update(torch.zeros(4, 64, dtype=torch.float32, device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(3, 5, 7), (1, 4097), (2, 33, 129)])
+def test_residual_arithmetic_on_sizes_the_vector_kernel_cannot_take(shape, dtype):
+    """pa_fbc_axpy's scalar form: sizes that are not multiples of 8 and storage offsets that are not
+    16-byte aligned give the same 16-bit results as the tensor operations they replace."""
+    from paraattention_b200.first_block_cache import utils as fbc
+
+    g = torch.Generator().manual_seed(sum(shape))
+    a = torch.randn(shape, generator=g).to(dtype).cuda()
+    b = torch.randn(shape, generator=g).to(dtype).cuda()
+    assert torch.equal(fbc._axpy(a, b, sub=True), a - b)
+    assert torch.equal(fbc._axpy(a, b, sub=False), a + b)
+    # same size, but storage that starts 2 bytes into an allocation
+    n = a.numel()
+    base_a, base_b = torch.empty(n + 1, dtype=dtype, device="cuda"), torch.empty(n + 1, dtype=dtype, device="cuda")
+    a2, b2 = base_a[1:].view(shape), base_b[1:].view(shape)
+    a2.copy_(a), b2.copy_(b)
+    assert torch.equal(fbc._axpy(a2, b2, sub=True), a - b)
+    with pytest.raises(NotImplementedError):
+        fbc._axpy(a.float(), b.float(), sub=True)
+
+
+def test_similarity_of_two_given_tensors_reads_no_third():
+    """are_two_tensors_similar passes no h0 to the kernel (the residual is t2 itself): same
+    decision and the same sums as forming t2 - 0 explicitly."""
+    from paraattention_b200.first_block_cache import utils as fbc
+
+    g = torch.Generator().manual_seed(3)
+    t1 = torch.randn(2, 512, 256, generator=g).to(torch.bfloat16).cuda()
+    t2 = (t1.float() * (1 + 0.07 * torch.randn(t1.shape, generator=g).cuda())).to(torch.bfloat16)
+    _, r_none = fbc.fused_residual_diff(t2, None, t1, store=False)
+    _, r_zero = fbc.fused_residual_diff(t2, torch.zeros_like(t2), t1, store=False)
+    assert torch.equal(r_none, r_zero)
+    ratio = float(r_none[4])
+    assert fbc.are_two_tensors_similar(t1, t2, threshold=ratio * 1.5)
+    assert not fbc.are_two_tensors_similar(t1, t2, threshold=ratio * 0.5)

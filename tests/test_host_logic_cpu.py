@@ -310,7 +310,10 @@ def _adapter_worker(rank, world, port, ret):
     import torch.distributed as dist
 
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    from paraattention_b200 import config
     from paraattention_b200.context_parallel.diffusers_adapters import parallelize_transformer
+
+    config.attention.allow_sdpa_fallback = True  # fp32 on CPU is outside the kernel's coverage
     from paraattention_b200.shape_models import FluxShapedPipeline, FluxShapedTransformer2DModel
     from paraattention_b200.shape_models_hunyuan import HunyuanVideoShapedTransformer3DModel
     from paraattention_b200.shape_models_video import WanShapedTransformer3DModel
@@ -342,7 +345,7 @@ def _adapter_worker(rank, world, port, ret):
 def test_adapters_restate_the_forward_exactly_on_one_rank():
     """With a single rank every shard is the whole tensor, so the adapters' re-stated forwards
     (patch grid, embeddings, output projection, un-patchify) must reproduce the models' own
-    outputs; runs on CPU in fp32, where attention falls through to PyTorch."""
+    outputs; runs on CPU in fp32 with the SDPA fallback switched on for the test."""
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
@@ -353,3 +356,121 @@ def test_adapters_restate_the_forward_exactly_on_one_rank():
     p.join(timeout=60)
     for name, e in errs.items():
         assert e < 1e-5, f"{name}: adapter output differs from the model's by {e:.3e}"
+
+
+def test_attention_outside_the_kernel_is_refused_unless_opted_in():
+    """Inside a mode an attention call the sm_100a kernel does not cover (here: CPU fp32) raises;
+    only config.attention.allow_sdpa_fallback hands it to PyTorch's SDPA."""
+    import torch.nn.functional as F
+
+    import paraattention_b200 as pa
+    from paraattention_b200 import config
+    from paraattention_b200.para_attn_interface import _local_attention, in_batch_attn_func
+
+    q = torch.randn(2, 2, 8, 64)
+    with pytest.raises(NotImplementedError, match="allow_sdpa_fallback"):
+        _local_attention(q, q, q)
+    with pytest.raises(NotImplementedError, match="allow_sdpa_fallback"):
+        with pa.InBatchAttnMode():
+            F.scaled_dot_product_attention(q, q, q)
+    with config.patch({"attention.allow_sdpa_fallback": True}):
+        torch.testing.assert_close(_local_attention(q, q, q), F.scaled_dot_product_attention(q, q, q))
+        # every batch element attends to the keys of all batch elements
+        folded = q.transpose(0, 1).reshape(1, 2, 16, 64)
+        want = F.scaled_dot_product_attention(folded, folded, folded).reshape(2, 2, 8, 64).transpose(0, 1)
+        torch.testing.assert_close(in_batch_attn_func(q, q, q), want)
+
+
+def test_unified_mode_refuses_a_custom_attn_func_on_a_parallel_mesh(monkeypatch):
+    """The reference forwards attn_func to ulysses_attn_func; with the exchange fused into the
+    kernel a foreign attention function cannot be wrapped, and dropping it silently would be
+    worse than saying so."""
+    import paraattention_b200 as pa
+    from paraattention_b200 import primitives as DP
+
+    mode = pa.UnifiedAttnMode.__new__(pa.UnifiedAttnMode)
+    mode._ulysses_mesh, mode._ring_mesh, mode._flat_group = object(), None, None
+    mode._skip_small_kv, mode._attn_func = False, (lambda *a, **k: None)
+    monkeypatch.setattr(DP, "get_world_size", lambda group=None: 2)
+    q = torch.randn(1, 2, 4, 64)
+    with pytest.raises(NotImplementedError, match="custom attn_func"):
+        mode._call_attn_func(q, q, q)
+
+
+def test_status_mirror_surfaces_a_sticky_timeout_and_resets():
+    """A device status word that an earlier launch set shows up as PaError(PA_ETIMEDOUT) on the
+    next check without any device synchronisation on the call path; reset() clears it."""
+    from paraattention_b200 import _lib as L
+    from paraattention_b200._status import StatusMirror
+
+    word = torch.zeros(1, dtype=torch.int32)
+    m = StatusMirror(word)
+    m.check()  # nothing reported
+    word[0] = L.PA_DEV_TIMEOUT_KV  # what a kernel's bounded wait writes when it gives up
+    m.check()  # the mirror has not been refreshed yet: still quiet
+    m.refresh()
+    with pytest.raises(L.PaError, match="key/value chunk") as e:
+        m.check()
+    assert e.value.code == L.PA_ETIMEDOUT
+    with pytest.raises(L.PaError):
+        m.check()  # sticky until reset
+    m.reset()
+    m.check()
+    assert int(word[0]) == 0
+
+
+def test_taylorseer_schedule_matches_the_reference_rule():
+    """Warm-up steps are computed, then every skip_interval-th step; an explicit map wins."""
+    from paraattention_b200.first_block_cache.taylorseer import TaylorSeer
+
+    seer = TaylorSeer(n_derivatives=3, warmup_steps=2, skip_interval_steps=3)
+    assert seer.ORDER == 4 and set(seer.state) == {"dY_prev", "dY_current"}
+    assert [seer.should_compute_full(s) for s in range(9)] == [True, True, False, False, True, False, False, True, False]
+    mapped = TaylorSeer(compute_step_map=[True, False, True])
+    assert [mapped.should_compute_full(s) for s in range(3)] == [True, False, True]
+    with pytest.raises(NotImplementedError):
+        TaylorSeer(n_derivatives=5)
+
+
+def _parallel_decision_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from paraattention_b200.first_block_cache.utils import _decide
+
+    rng = np.random.default_rng(7)
+    numel = 4096
+    cases = []
+    for thr in (0.05, 0.08, 0.12):
+        for _ in range(6):
+            # per-rank fp32 sums as the cache kernel leaves them, chosen so that ratios land on both sides of thr
+            sd = rng.uniform(0.02, 0.2, size=world) * numel
+            sp = rng.uniform(0.8, 1.2, size=world) * numel
+            cases.append((thr, sd, sp))
+    out = []
+    for thr, sd, sp in cases:
+        md = O.bf16_round(np.float32(sd[rank] / numel))
+        mp_ = O.bf16_round(np.float32(sp[rank] / numel))
+        result = torch.tensor([sd[rank], sp[rank], float(md), float(mp_), 0.0], dtype=torch.float32)
+        got = _decide(result, torch.bfloat16, thr, parallelized=True)
+        want = O.fbc_decision(list(sd), list(sp), numel, thr)
+        out.append((got, want))
+    if rank == 0:
+        ret.put(out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_parallel_cache_decision_matches_the_oracle_over_gloo():
+    """_decide(parallelized=True): each rank's two rounded means are averaged over the group before
+    the bf16 division (src/para_attn/first_block_cache/utils.py:230-232); two ranks over gloo
+    against the oracle's restatement, on thresholds that split the cases."""
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    procs = [ctx.Process(target=_parallel_decision_worker, args=(r, 2, 29671, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = ret.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+    assert all(g == w for g, w in out), out
+    assert {w for _, w in out} == {True, False}, "the cases must cover both outcomes"
