@@ -120,10 +120,10 @@ typedef struct pa_cp_attn_args {
     int32_t* status;
     uint64_t wait_limit_ns;
     /* Fused exchange (may be NULL): the first fused_push->ctas_per_dest CTAs of this launch
-     * (capped by the grid size and 128) perform the pushes described by *fused_push before they
-     * take up attention tiles, and add 1 each to every destination's counter. The consumers'
-     * flag_expect must therefore grow by that CTA count per call. The host struct is read
-     * during the call only. */
+     * (capped by the grid size and the number of SMs, so that all of them are resident at once)
+     * perform the pushes described by *fused_push before they take up attention tiles, and add
+     * 1 each to every destination's counter. The consumers' flag_expect must therefore grow by
+     * that CTA count per call. The host struct is read during the call only. */
     const struct pa_cp_push_args* fused_push;
     /* Zero-copy own shard (each may be NULL): when given, query chunk q_first (key/value chunk
      * kv_first) is not read from the staging buffer but straight from this rank's own tensor,
@@ -163,6 +163,42 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);
  * (src/para_attn/ops/__init__.py:271-283). */
 int pa_pack_key_mask(const uint8_t* mask, int64_t batch_stride, int32_t batch, int32_t n_chunks, int32_t rows,
                      uint64_t* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * The neighbours of attention in a transformer block, one HBM-bound pass instead of a dozen
+ * tensor operations: per-head RMSNorm of q and k with a per-channel weight, rotary embedding of
+ * both, and placement of q, k, v into the buffers attention reads. No single counterpart in
+ * the reference: it is what the models' attention processors do between the q/k/v projections
+ * and the scaled_dot_product_attention call that the modes of
+ * src/para_attn/para_attn_interface.py:279-495 intercept.
+ *
+ * q, k, v: [batch, rows, heads, head_dim] with element strides (batch, row, head), head_dim
+ * contiguous (64 or 128). v and v_out may be NULL (then v is not touched). q_weight / k_weight:
+ * [head_dim] in the tensors' dtype, or NULL (no normalisation). cos / sin: fp32 tables
+ * [>= table_row0 + rows, head_dim] whose row table_row0 + r belongs to row r, or both NULL.
+ * Rotation pairs are the adjacent elements (2i, 2i+1): out[2i] = x[2i] cos[2i] - x[2i+1] sin[2i],
+ * out[2i+1] = x[2i+1] cos[2i+1] + x[2i] sin[2i+1]. Outputs may alias nothing but themselves.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct pa_qkv_prep_args {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* q_out;
+    void* k_out;
+    void* v_out;
+    int64_t q_stride[3], k_stride[3], v_stride[3];              /* element strides (batch, row, head) */
+    int64_t q_out_stride[3], k_out_stride[3], v_out_stride[3];
+    const void* q_weight;
+    const void* k_weight;
+    const float* cos;
+    const float* sin;
+    int64_t table_row0;
+    int32_t batch, rows, heads, head_dim;
+    int32_t dtype;           /* pa_dtype */
+    float eps;
+} pa_qkv_prep_args;
+
+int pa_qkv_prep(const pa_qkv_prep_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Exchange. Replaces the NCCL all_to_all_single calls of _sdpa_input_all_to_all /

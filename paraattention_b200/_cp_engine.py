@@ -103,12 +103,13 @@ class CpPlan:
                 dest = self.flat(u_d, r_d)
                 if skip_self and dest == self.rank:
                     continue
+                # Q only to my Ulysses group (first: a consumer needs it before any key); chunk slot =
+                # my ulysses index
+                if r_d == self.r:
+                    jobs.append(PushJobSpec("q", dest, u_d * hl, hl, self.u))
                 # K and V of my shard go to every rank; chunk slot = my flat rank
                 jobs.append(PushJobSpec("k", dest, u_d * hl, hl, self.rank))
                 jobs.append(PushJobSpec("v", dest, u_d * hl, hl, self.rank))
-                # Q only to my Ulysses group; chunk slot = my ulysses index
-                if r_d == self.r:
-                    jobs.append(PushJobSpec("q", dest, u_d * hl, hl, self.u))
         return jobs
 
     def q_sources(self) -> List[int]:
@@ -236,10 +237,10 @@ def build_push_args(plan: CpPlan, ws: Workspace, par: int, q, k, v, ctas: int,
     return pa
 
 
-def fused_push_ctas(plan: CpPlan, B: int, sq: int, ctas: int) -> int:
+def fused_push_ctas(plan: CpPlan, B: int, sq: int, ctas: int, sm_count: int = 148) -> int:
     """How many leading CTAs of the attention grid push (the library applies the same cap)."""
     grid = ((sq + 255) // 256) * plan.local_heads * B * plan.ulysses
-    return max(1, min(ctas, grid, 128))
+    return max(1, min(ctas, grid, sm_count))
 
 
 def launch_attention(plan: CpPlan, ws: Workspace, par: int, shape, dtype: torch.dtype, skv: int, scale: float,
@@ -413,6 +414,7 @@ class CpEngine:
         ws, st = self.ws, self.state
         par = st.calls & 1
         st.calls += 1
+        sms = _sm_count(self.device)
         ctas = config.cp.push_ctas_per_dest
         if ctas <= 0:
             # automatic: about one pushing CTA per 5 MB this rank has to send, between 16 and 64
@@ -423,7 +425,7 @@ class CpEngine:
             ctas = (sent + (5 << 20) - 1) // (5 << 20)
             # SMs that the last, partly filled wave of the grid leaves idle can push for free
             grid = ((sq + 255) // 256) * hl * B * self.ulysses
-            spare = (-grid) % _sm_count(self.device)
+            spare = (-grid) % sms
             ctas = max(16, min(64, max(ctas, min(spare, 48))))
         wait_ns = config.cp.wait_limit_ns
         scale = (1.0 / math.sqrt(D)) if scale is None else float(scale)
@@ -435,7 +437,7 @@ class CpEngine:
         # on shapes, strides and the staging parity: they are built once and then only the
         # pointers and the expected counter value are patched (the host side of a 30 us kernel
         # must not cost more than the kernel).
-        n_push = fused_push_ctas(plan, B, sq, ctas)
+        n_push = fused_push_ctas(plan, B, sq, ctas, sms)
         st.arrive_expect[par] += n_push
         out_local = None
         if self.ulysses == 1:
@@ -445,8 +447,8 @@ class CpEngine:
             from . import ops as _ops
 
             key_bits = _ops.pack_key_mask(key_mask, self.world, skv)
-        key = (B, H, sq, skv, D, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(), is_causal,
-               key_bits is not None)
+        key = (B, H, sq, skv, D, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(),
+               is_causal, key_bits is not None)
         ent = self._launch_cache.get(key)
         if ent is None:
             push = build_push_args(plan, ws, par, q, k, v, n_push)

@@ -87,6 +87,19 @@ class CpPushArgs(C.Structure):
     ]
 
 
+class QkvPrepArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("q_out", C.c_void_p), ("k_out", C.c_void_p), ("v_out", C.c_void_p),
+        ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
+        ("q_out_stride", C.c_int64 * 3), ("k_out_stride", C.c_int64 * 3), ("v_out_stride", C.c_int64 * 3),
+        ("q_weight", C.c_void_p), ("k_weight", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
+        ("table_row0", C.c_int64),
+        ("batch", C.c_int32), ("rows", C.c_int32), ("heads", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("eps", C.c_float),
+    ]
+
+
 _lib = None
 
 
@@ -106,6 +119,8 @@ def load() -> C.CDLL:
     lib.pa_version.restype = C.c_int
     lib.pa_attn_fwd.restype = C.c_int
     lib.pa_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
+    lib.pa_qkv_prep.restype = C.c_int
+    lib.pa_qkv_prep.argtypes = [C.POINTER(QkvPrepArgs), C.c_void_p]
     lib.pa_cp_attn_fwd.restype = C.c_int
     lib.pa_cp_attn_fwd.argtypes = [C.POINTER(CpAttnArgs), C.c_void_p]
     lib.pa_taylor_update.restype = C.c_int

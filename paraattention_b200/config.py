@@ -21,6 +21,9 @@ class attention:
     force_dispatch_to_custom_ops = os.getenv("PARA_ATTN_FORCE_DISPATCH_TO_CUSTOM_OPS") == "1"
     allow_reduced_precision_compute = os.getenv("PARA_ATTN_ALLOW_REDUCED_PRECISION_COMPUTE") == "1"
     allow_sdpa_fallback = os.getenv("PA_B200_ALLOW_SDPA_FALLBACK") == "1"
+    # the shape-only transformers of this package prepare q, k, v with the fused kernel
+    # (ops.qkv_prepare) instead of a chain of tensor operations when their tensors allow it
+    fuse_qkv_prepare = os.getenv("PA_B200_FUSE_QKV_PREPARE", "1") == "1"
 
 
 class cp:

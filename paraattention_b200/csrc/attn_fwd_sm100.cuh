@@ -289,12 +289,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem = ctl->tmem_base;
 
     // ---- which work unit: (batch, head, query chunk, pair of query tiles) -------------------
-    // The CTAs that push first (the leading ones of the grid) take the LAST work units: those
-    // belong to the query chunk that arrives last (and, in a causal run, to the short early
-    // tiles), so the units that can start at once go to CTAs that start at once.
     const int pairs_per_chunk = (p.q_rows + 2 * kTileM - 1) / (2 * kTileM);
     int unit = blockIdx.x;
     if (push.n_push_ctas > 0) {
+        // CTAs that push before they compute take the LAST work units (the query chunk that
+        // arrives last), so the units that can start at once go to CTAs that start at once
         unit -= push.n_push_ctas;
         if (unit < 0) unit += gridDim.x;
     }
@@ -326,11 +325,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     // Fused exchange: the leading CTAs of the grid (always resident in the first wave, and
     // waiting for nobody) first store this rank's Q/K/V head-slices into the staging buffers
-    // of the ranks that consume them - own buffer first, then the ranks below in descending
-    // order (a consumer walks its chunks upwards from its own rank, so the first chunk it
-    // needs from a peer is the one that peer sends first) - and only then take up their
-    // attention tiles. Every other CTA starts computing at once and
-    // meets a chunk only when it needs it.
+    // of the ranks that consume them - the ranks below first, in descending order (a consumer
+    // walks its chunks upwards from its own rank, so the first chunk it needs from a peer is the
+    // one that peer sends first) - and only then take up their attention tiles. Every other CTA
+    // starts computing at once and meets a chunk only when it needs it. (Letting two spare warps
+    // of every first-wave CTA copy in the background instead was measured slower on 2 and on 8
+    // GPUs: the copy then takes most of the kernel's duration and the first remote chunk is late.)
     if (push.n_push_ctas > 0 && static_cast<int>(blockIdx.x) < push.n_push_ctas) {
         for (int di = 0; di < push.n_dest; ++di) {
             int dest = push.first_dest - di;

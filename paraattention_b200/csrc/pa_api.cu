@@ -14,6 +14,7 @@
 #include "fbc_sm100.cuh"
 #include "key_mask_sm100.cuh"
 #include "merge_sm100.cuh"
+#include "qkv_prep_sm100.cuh"
 #include "taylor_sm100.cuh"
 
 namespace {
@@ -358,7 +359,7 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
         // pushers must all be resident at once: never more than the grid or one wave of SMs
         int n = a->fused_push->ctas_per_dest;
         if (n > grid) n = int(grid);
-        if (n > 128) n = 128;
+        if (n > sm_count()) n = sm_count();
         push.n_push_ctas = n;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -597,6 +598,60 @@ int pa_fbc_axpy(const void* a, const void* b, void* out, int64_t numel, int32_t 
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(PA_ECUDA, "axpy launch: %s", cudaGetErrorString(e));
+    return PA_OK;
+}
+
+int pa_qkv_prep(const pa_qkv_prep_args* a, void* stream) {
+    if (a == nullptr) return fail(PA_EINVAL, "qkv_prep: args is NULL");
+    if (a->batch <= 0 || a->rows <= 0 || a->heads <= 0) return fail(PA_EINVAL, "qkv_prep: batch, rows, heads must be positive");
+    if (a->head_dim != 64 && a->head_dim != 128) return fail(PA_ENOTSUP, "qkv_prep: head_dim %d: only 64 and 128 are built", a->head_dim);
+    if (a->dtype != PA_BF16 && a->dtype != PA_F16) return fail(PA_EINVAL, "qkv_prep: dtype must be PA_BF16 or PA_F16");
+    if ((a->cos == nullptr) != (a->sin == nullptr)) return fail(PA_EINVAL, "qkv_prep: cos and sin go together");
+    if (!(a->eps >= 0.f)) return fail(PA_EINVAL, "qkv_prep: eps must not be negative");
+    pa::QkvPrepParams p;
+    memset(&p, 0, sizeof(p));
+    const unsigned align = a->head_dim == 128 ? 7u : 3u;  // one lane moves 8 or 4 bytes
+    const void* src[3] = {a->q, a->k, a->v};
+    void* dst[3] = {a->q_out, a->k_out, a->v_out};
+    const int64_t* ss[3] = {a->q_stride, a->k_stride, a->v_stride};
+    const int64_t* ds[3] = {a->q_out_stride, a->k_out_stride, a->v_out_stride};
+    for (int i = 0; i < 3; ++i) {
+        if (src[i] == nullptr) {
+            if (i < 2) return fail(PA_EINVAL, "qkv_prep: q and k must be non-NULL");
+            continue;
+        }
+        if (dst[i] == nullptr) return fail(PA_EINVAL, "qkv_prep: output %d is NULL", i);
+        if ((reinterpret_cast<uintptr_t>(src[i]) & align) || (reinterpret_cast<uintptr_t>(dst[i]) & align))
+            return fail(PA_EINVAL, "qkv_prep: tensor %d: base pointers must be %u-byte aligned", i, align + 1);
+        for (int d = 0; d < 3; ++d)
+            if (((ss[i][d] * 2) & align) || ((ds[i][d] * 2) & align))
+                return fail(PA_EINVAL, "qkv_prep: tensor %d: byte strides must be multiples of %u", i, align + 1);
+        p.src[i] = static_cast<const uint16_t*>(src[i]);
+        p.dst[i] = static_cast<uint16_t*>(dst[i]);
+        p.s_sb[i] = ss[i][0]; p.s_ss[i] = ss[i][1]; p.s_sh[i] = ss[i][2];
+        p.d_sb[i] = ds[i][0]; p.d_ss[i] = ds[i][1]; p.d_sh[i] = ds[i][2];
+    }
+    p.w[0] = static_cast<const uint16_t*>(a->q_weight);
+    p.w[1] = static_cast<const uint16_t*>(a->k_weight);
+    p.cos = a->cos;
+    p.sin = a->sin;
+    p.table_row0 = a->table_row0;
+    p.batch = a->batch; p.rows = a->rows; p.heads = a->heads;
+    p.eps = a->eps;
+    const long long total = static_cast<long long>(a->batch) * a->rows * a->heads;
+    long long blocks = (total + pa::kPrepThreads / 32 - 1) / (pa::kPrepThreads / 32);
+    const long long cap = static_cast<long long>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (a->dtype == PA_BF16) {
+        if (a->head_dim == 128) pa::qkv_prep_kernel<true, 128><<<int(blocks), pa::kPrepThreads, 0, s>>>(p);
+        else pa::qkv_prep_kernel<true, 64><<<int(blocks), pa::kPrepThreads, 0, s>>>(p);
+    } else {
+        if (a->head_dim == 128) pa::qkv_prep_kernel<false, 128><<<int(blocks), pa::kPrepThreads, 0, s>>>(p);
+        else pa::qkv_prep_kernel<false, 64><<<int(blocks), pa::kPrepThreads, 0, s>>>(p);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(PA_ECUDA, "qkv_prep launch: %s", cudaGetErrorString(e));
     return PA_OK;
 }
 

@@ -27,6 +27,7 @@ __all__ = [
     "pack_key_mask",
     "merge_out_lse_",
     "raw_attention_forward",
+    "qkv_prepare",
 ]
 
 _DTYPES = {torch.bfloat16: L.PA_BF16, torch.float16: L.PA_F16}
@@ -248,6 +249,72 @@ def cp_attention_forward(
 def _(query, key, value, key_mask, is_causal, scale, engine_id):
     B, H, Sq, D = query.shape
     return query.new_empty((B, Sq, H, D)).transpose(1, 2)
+
+
+def qkv_prepare(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor], q_weight: Optional[torch.Tensor] = None,
+                k_weight: Optional[torch.Tensor] = None, rotary: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, *,
+                eps: float = 1e-6, out: Optional[Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]] = None,
+                row_offset: int = 0):
+    """What a transformer block does to q, k, v between their projections and attention, in one
+    launch of pa_qkv_prep: per-head RMSNorm of q and k (``x * rsqrt(mean(x^2) + eps)`` rounded to
+    the dtype, times the per-channel weight), rotary embedding of both (``rotary = (cos, sin)``,
+    fp32 [rows of the whole sequence, D]; adjacent elements are the rotation pairs), and placement
+    into [B, H, S, D] views of [B, S, H, D] buffers - the layout the attention ops like best.
+
+    q, k, v: [B, H, S, D] views with contiguous D (projection outputs viewed per head). With
+    ``out = (q_buf, k_buf, v_buf)`` ([B, H, S_total, D] views, S_total >= row_offset + S) the rows
+    [row_offset, row_offset + S) of those buffers are written and the rotary tables are read
+    from row ``row_offset`` on, which is how the streams of a joint-attention block land in one
+    buffer without a concatenation. Returns the three destination views (the written rows)."""
+    assert q.device.type == "cuda", "Must be CUDA tensors"
+    assert q.ndim == 4 and k.shape == q.shape and (v is None or v.shape == q.shape), "q, k, v must be [B, H, S, D] alike"
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or (v is not None and v.dtype != q.dtype):
+        raise NotImplementedError(f"qkv_prepare dtype {q.dtype}: only bfloat16 and float16 are built")
+    B, H, S, D = q.shape
+    if D not in (64, 128):
+        raise NotImplementedError(f"head_dim {D}: only 64 and 128 are built")
+    ins = [q, k, v]
+    for i, t in enumerate(ins):
+        if t is not None and t.stride(-1) != 1:
+            ins[i] = t.contiguous()
+    if out is None:
+        out = tuple(torch.empty((B, S, H, D), dtype=q.dtype, device=q.device).transpose(1, 2) if t is not None else None
+                    for t in ins)
+        row_offset_out = 0
+    else:
+        row_offset_out = row_offset
+        for t, o in zip(ins, out):
+            assert (t is None) == (o is None)
+            assert o is None or (o.ndim == 4 and o.shape[0] == B and o.shape[1] == H and o.shape[3] == D and
+                                 o.shape[2] >= row_offset + S and o.stride(-1) == 1 and o.dtype == q.dtype)
+    a = L.QkvPrepArgs()
+    dsts = []
+    for name, t, o in zip("qkv", ins, out):
+        if t is None:
+            dsts.append(None)
+            continue
+        dst = o[:, :, row_offset_out:row_offset_out + S]
+        dsts.append(dst)
+        setattr(a, name, t.data_ptr())
+        setattr(a, name + "_out", dst.data_ptr())
+        for j, dim in enumerate((0, 2, 1)):  # (batch, row, head)
+            getattr(a, name + "_stride")[j] = t.stride(dim)
+            getattr(a, name + "_out_stride")[j] = dst.stride(dim)
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            assert w.shape == (D,) and w.dtype == q.dtype and w.is_contiguous() and w.device == q.device
+            setattr(a, name, w.data_ptr())
+    if rotary is not None:
+        cos, sin = rotary
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous() and sin.is_contiguous()
+        assert cos.shape == sin.shape and cos.ndim == 2 and cos.shape[1] == D and cos.shape[0] >= row_offset + S
+        a.cos, a.sin = cos.data_ptr(), sin.data_ptr()
+    a.table_row0 = row_offset
+    a.batch, a.rows, a.heads, a.head_dim = B, S, H, D
+    a.dtype = _DTYPES[q.dtype]
+    a.eps = eps
+    L.check(L.load().pa_qkv_prep(C.byref(a), torch.cuda.current_stream(q.device).cuda_stream))
+    return tuple(dsts)
 
 
 def merge_out_lse_(acc_out: torch.Tensor, acc_lse: torch.Tensor, block_out: torch.Tensor,

@@ -52,6 +52,66 @@ def _rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor
     return (x.float() * cos + rot.float() * sin).to(x.dtype)
 
 
+def _joint_qkv(streams, rotary, rotary_rows=None):
+    """q, k, v of one attention call from the projection outputs of its streams.
+
+    ``streams``: list of ``(q, k, v, q_weight, k_weight)`` in sequence order, q/k/v [B, S_i, H*D]
+    projection outputs (any row stride), weights [D] or None. ``rotary``: (cos, sin) or None;
+    ``rotary_rows = (first, count)`` limits the rotation to those rows of the joint sequence,
+    table row 0 belonging to joint row ``first`` (default: all rows). Returns [B, H, sum S_i, D] views.
+
+    On CUDA bf16/f16 tensors each stream is one launch of the fused kernel (three when only a
+    part of it rotates), which normalises, rotates and writes into the joint buffers
+    (``config.attention.fuse_qkv_prepare``); otherwise the same arithmetic runs as the chain of
+    tensor operations below."""
+    from . import config
+
+    q0 = streams[0][0]
+    total = sum(st[0].shape[1] for st in streams)
+    first, count = (0, total) if rotary_rows is None else rotary_rows
+    if config.attention.fuse_qkv_prepare and q0.device.type == "cuda" and q0.dtype in (torch.bfloat16, torch.float16):
+        from . import ops
+
+        B, H = q0.shape[0], q0.shape[2] // HEAD_DIM
+        bufs = tuple(torch.empty((B, total, H, HEAD_DIM), dtype=q0.dtype, device=q0.device).transpose(1, 2)
+                     for _ in range(3))
+        off = 0
+        for q, k, v, wq, wk in streams:
+            rows = q.shape[1]
+            lo, hi = max(off, first), min(off + rows, first + count)  # joint rows of this stream that rotate
+            if rotary is None or hi <= lo:
+                segments = [(0, rows, False)]
+            else:
+                segments = [(0, lo - off, False), (lo - off, hi - off, True), (hi - off, rows, False)]
+            for a, b, rotate in segments:
+                if b <= a:
+                    continue
+                joint_row = off + a
+                table_row = joint_row - first if rotate else joint_row
+                # destination views cut so that their row index equals the table row index
+                dst = tuple(buf[:, :, joint_row - table_row:] for buf in bufs)
+                ops.qkv_prepare(_split_heads(q[:, a:b]), _split_heads(k[:, a:b]), _split_heads(v[:, a:b]), wq, wk,
+                                rotary if rotate else None, out=dst, row_offset=table_row)
+            off += rows
+        return bufs
+    qs, ks, vs = [], [], []
+    for q, k, v, wq, wk in streams:
+        q, k, v = _split_heads(q), _split_heads(k), _split_heads(v)
+        qs.append(_rms(q, wq) if wq is not None else q)
+        ks.append(_rms(k, wk) if wk is not None else k)
+        vs.append(v)
+    q, k, v = (torch.cat(t, dim=2) if len(t) > 1 else t[0] for t in (qs, ks, vs))
+    if rotary is not None:
+        cos, sin = rotary
+        if first == 0 and count == total:
+            q, k = _rope(q, cos, sin), _rope(k, cos, sin)
+        else:
+            sl = slice(first, first + count)
+            q = torch.cat([q[:, :, :first], _rope(q[:, :, sl], cos, sin), q[:, :, first + count:]], dim=2)
+            k = torch.cat([k[:, :, :first], _rope(k[:, :, sl], cos, sin), k[:, :, first + count:]], dim=2)
+    return q, k, v
+
+
 def _rope_table(positions: torch.Tensor, axes_dim=(16, 56, 56), theta: float = 10000.0):
     """positions: [S, 3] -> (cos, sin) of shape [S, sum(axes_dim)] with pairwise-repeated frequencies."""
     outs = []
@@ -146,6 +206,12 @@ class _JointStream(nn.Module):
         q, k, v = _split_heads(q), _split_heads(k), _split_heads(v)
         return _rms(q, self.q_norm), _rms(k, self.k_norm), v, (gate, shift2, scale2, gate2)
 
+    def qkv_stream(self, x, temb):
+        """The raw projections and norm weights as a stream of ``_joint_qkv``, plus the modulation."""
+        shift, scale, gate, shift2, scale2, gate2 = self.mod(temb)
+        q, k, v = self.qkv(_norm(x) * (1 + scale) + shift).chunk(3, dim=-1)
+        return (q, k, v, self.q_norm, self.k_norm), (gate, shift2, scale2, gate2)
+
     def finish(self, x, attn, mods):
         gate, shift2, scale2, gate2 = mods
         x = x + gate * self.out(attn)
@@ -159,12 +225,9 @@ class FluxDualStreamBlock(nn.Module):
         self.txt = _JointStream(dim, mlp_ratio)
 
     def forward(self, hidden_states, encoder_hidden_states, temb, image_rotary_emb=None, **kwargs):
-        qi, ki, vi, mi = self.img.qkv_heads(hidden_states, temb)
-        qt, kt, vt, mt = self.txt.qkv_heads(encoder_hidden_states, temb)
-        q, k, v = torch.cat([qt, qi], dim=2), torch.cat([kt, ki], dim=2), torch.cat([vt, vi], dim=2)
-        if image_rotary_emb is not None:
-            q, k = _rope(q, *image_rotary_emb), _rope(k, *image_rotary_emb)
-        attn = _attention(q, k, v)
+        img, mi = self.img.qkv_stream(hidden_states, temb)
+        txt, mt = self.txt.qkv_stream(encoder_hidden_states, temb)
+        attn = _attention(*_joint_qkv([txt, img], image_rotary_emb))
         n_txt = encoder_hidden_states.shape[1]
         encoder_hidden_states = self.txt.finish(encoder_hidden_states, attn[:, :n_txt], mt)
         hidden_states = self.img.finish(hidden_states, attn[:, n_txt:], mi)
@@ -185,10 +248,7 @@ class FluxSingleStreamBlock(nn.Module):
         shift, scale, gate = self.mod(temb)
         qkv, mlp = self.qkv_mlp(_norm(hidden_states) * (1 + scale) + shift).split([3 * self.dim, self.qkv_mlp.out_features - 3 * self.dim], dim=-1)
         q, k, v = qkv.chunk(3, dim=-1)
-        q, k, v = _rms(_split_heads(q), self.q_norm), _rms(_split_heads(k), self.k_norm), _split_heads(v)
-        if image_rotary_emb is not None:
-            q, k = _rope(q, *image_rotary_emb), _rope(k, *image_rotary_emb)
-        attn = _attention(q, k, v)
+        attn = _attention(*_joint_qkv([(q, k, v, self.q_norm, self.k_norm)], image_rotary_emb))
         return hidden_states + gate * self.out(torch.cat([attn, F.gelu(mlp, approximate="tanh")], dim=-1))
 
 

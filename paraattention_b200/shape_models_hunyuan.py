@@ -12,7 +12,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .shape_models import (HEAD_DIM, ShapeModelOutput, _attention, _DeviceMixin, _Modulation, _norm, _rms, _rope,
-                           _rope_table, _split_heads, _TimeTextEmbed, _JointStream)
+                           _joint_qkv, _rope_table, _split_heads, _TimeTextEmbed, _JointStream)
 from .shape_models_video import _grid_positions
 
 
@@ -46,16 +46,6 @@ class _ContextEmbedder(nn.Module):
         return self.proj(encoder_hidden_states)
 
 
-def _joint_rope(q, k, n_img, image_rotary_emb):
-    """Rotary embedding on the video tokens (the first n_img of the joint sequence) only."""
-    if image_rotary_emb is None:
-        return q, k
-    cos, sin = image_rotary_emb
-    q = torch.cat([_rope(q[:, :, :n_img], cos, sin), q[:, :, n_img:]], dim=2)
-    k = torch.cat([_rope(k[:, :, :n_img], cos, sin), k[:, :, n_img:]], dim=2)
-    return q, k
-
-
 class HunyuanDualStreamBlock(nn.Module):
     def __init__(self, dim: int, mlp_ratio: float = 4.0):
         super().__init__()
@@ -63,11 +53,11 @@ class HunyuanDualStreamBlock(nn.Module):
         self.txt = _JointStream(dim, mlp_ratio)
 
     def forward(self, hidden_states, encoder_hidden_states, temb, attention_mask=None, image_rotary_emb=None):
-        qi, ki, vi, mi = self.img.qkv_heads(hidden_states, temb)
-        qt, kt, vt, mt = self.txt.qkv_heads(encoder_hidden_states, temb)
+        img, mi = self.img.qkv_stream(hidden_states, temb)
+        txt, mt = self.txt.qkv_stream(encoder_hidden_states, temb)
         n_img = hidden_states.shape[1]
-        q, k, v = torch.cat([qi, qt], dim=2), torch.cat([ki, kt], dim=2), torch.cat([vi, vt], dim=2)
-        q, k = _joint_rope(q, k, n_img, image_rotary_emb)
+        # rotary embedding on the video tokens (the first n_img of the joint sequence) only
+        q, k, v = _joint_qkv([img, txt], image_rotary_emb, rotary_rows=(0, n_img))
         attn = F.scaled_dot_product_attention(q, k, v, attn_mask=attention_mask).transpose(1, 2).flatten(2)
         hidden_states = self.img.finish(hidden_states, attn[:, :n_img], mi)
         encoder_hidden_states = self.txt.finish(encoder_hidden_states, attn[:, n_img:], mt)
@@ -89,8 +79,7 @@ class HunyuanSingleStreamBlock(nn.Module):
         shift, scale, gate = self.mod(temb)
         qkv, mlp = self.qkv_mlp(_norm(x) * (1 + scale) + shift).split([3 * self.dim, self.mlp], dim=-1)
         q, k, v = qkv.chunk(3, dim=-1)
-        q, k, v = _rms(_split_heads(q), self.q_norm), _rms(_split_heads(k), self.k_norm), _split_heads(v)
-        q, k = _joint_rope(q, k, n_img, image_rotary_emb)
+        q, k, v = _joint_qkv([(q, k, v, self.q_norm, self.k_norm)], image_rotary_emb, rotary_rows=(0, n_img))
         attn = F.scaled_dot_product_attention(q, k, v, attn_mask=attention_mask).transpose(1, 2).flatten(2)
         x = x + gate * self.out(torch.cat([attn, F.gelu(mlp, approximate="tanh")], dim=-1))
         return x[:, :n_img], x[:, n_img:]

@@ -12,7 +12,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .shape_models import (HEAD_DIM, ShapeModelOutput, _attention, _DeviceMixin, _FeedForward, _Modulation, _norm,
-                           _rms, _rope, _rope_table, _split_heads, _timestep_embedding, _TimeTextEmbed)
+                           _joint_qkv, _rms, _rope, _rope_table, _split_heads, _timestep_embedding, _TimeTextEmbed)
 
 
 def _grid_positions(frames: int, height: int, width: int, device) -> torch.Tensor:
@@ -65,8 +65,8 @@ class WanShapedBlock(nn.Module):
             hidden_states.dtype).chunk(6, dim=1)
         cos, sin = rotary_emb[0, 0].chunk(2, dim=-1)
         q, k, v = self.qkv(_norm(hidden_states) * (1 + scale) + shift).chunk(3, dim=-1)
-        q, k, v = _rms(_split_heads(q), self.q_norm), _rms(_split_heads(k), self.k_norm), _split_heads(v)
-        hidden_states = hidden_states + gate * self.out(_attention(_rope(q, cos, sin), _rope(k, cos, sin), v))
+        q, k, v = _joint_qkv([(q, k, v, self.q_norm, self.k_norm)], (cos.contiguous(), sin.contiguous()))
+        hidden_states = hidden_states + gate * self.out(_attention(q, k, v))
         # cross-attention to the prompt
         cq = _split_heads(self.cross_q(_norm(hidden_states)))
         ck, cv = self.cross_kv(encoder_hidden_states).chunk(2, dim=-1)
