@@ -532,8 +532,13 @@ def engine_by_id(i: int) -> CpEngine:
 
 def check_device_status() -> None:
     """Raise if any attention kernel of this process reported a timed-out wait (synchronises)."""
+    from . import _peer_gather
+
     for eng in _engines.values():
         eng.check_status()
+    for g in _peer_gather.all_gathers():
+        if g.status is not None:
+            g.status.check_now()
     for mirror in _status.all_mirrors():
         mirror.check_now()
 
@@ -541,7 +546,11 @@ def check_device_status() -> None:
 def reset_device_status() -> None:
     """Clear every status word and resynchronise the exchange counters (collective over each
     engine's group): the way back to a usable state after a ``PaError(PA_ETIMEDOUT)``."""
+    from . import _peer_gather
+
     for eng in _engines.values():
         eng.reset()
+    for g in _peer_gather.all_gathers():
+        g.reset()
     for mirror in _status.all_mirrors():
         mirror.reset()

@@ -31,6 +31,8 @@ class cp:
 
     # how many leading CTAs of the attention grid do the exchange (0 = choose from the bytes to send)
     push_ctas_per_dest = int(os.getenv("PA_B200_PUSH_CTAS", "0"))
+    # get_complete_tensor (the gather at the exit of a parallelised forward) as peer stores
+    peer_gather = os.getenv("PA_B200_PEER_GATHER", "1") == "1"
     # Ulysses output: hand out the staging buffer itself instead of a private copy. The tensor is
     # then overwritten by the second-next attention call of the same mesh: only for callers that
     # consume an attention result before issuing two more (every transformer block does).

@@ -16,6 +16,8 @@ import torch.distributed as dist
 import torch.distributed._functional_collectives as funcol
 from torch.distributed.distributed_c10d import _get_default_group
 
+from . import config
+
 
 # ------------------------------------------------------------------------------------------
 # groups
@@ -102,6 +104,18 @@ def get_assigned_chunk(tensor: torch.Tensor, dim: int = 0, idx: Optional[int] = 
 
 
 def get_complete_tensor(tensor: torch.Tensor, *, dim: int = 0, group=None) -> torch.Tensor:
-    """Inverse of ``get_assigned_chunk``: the shards of all ranks concatenated along ``dim``."""
+    """Inverse of ``get_assigned_chunk``: the shards of all ranks concatenated along ``dim``
+    (src/para_attn/primitives.py:139-148). CUDA tensors on an NCCL group of up to eight ranks go
+    through peer stores into every rank's result buffer (``_peer_gather``; switch off with
+    ``config.cp.peer_gather``); everything else takes the transpose -> all_gather -> transpose of
+    the reference."""
+    pg = get_group(group)
+    if (tensor.device.type == "cuda" and get_world_size(pg) > 1 and config.cp.peer_gather
+            and dist.get_backend(pg) == "nccl" and get_world_size(pg) <= 8 and tensor.numel() > 0):
+        from . import _peer_gather
+
+        out = _peer_gather.get_gather(pg, tensor.device).gather(tensor, dim)
+        if out is not None:
+            return out
     moved = tensor.transpose(0, dim).contiguous()  # the gather concatenates along dim 0
     return all_gather_tensor_sync(moved, gather_dim=0, group=group).transpose(0, dim)

@@ -277,3 +277,55 @@ def test_multi_gpu_processes(mode):
     ref, _ = O.sdpa_with_lse(q.float().numpy(), k.float().numpy(), v.float().numpy(),
                              is_causal=mode.endswith("causal"), key_mask=key_mask)
     assert_attention_close(torch.from_numpy(full), ref, f"{mode} world {world}")
+
+
+def _gather_worker(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import paraattention_b200 as pa
+    from paraattention_b200 import config
+    from paraattention_b200 import primitives as DP
+
+    ok = True
+    cases = [((2, 576, 64), -2, torch.bfloat16), ((1, 300, 128), 1, torch.float32), ((4, 64, 8, 16), 0, torch.float16),
+             ((1, 4095, 64), -2, torch.bfloat16), ((2, 7, 3), 1, torch.bfloat16)]  # the last one has no whole rows: NCCL path
+    for rep in range(3):  # both parities of the result buffers and the growing counters
+        for shape, dim, dtype in cases:
+            g = torch.Generator().manual_seed(rank * 100 + rep)
+            shard = torch.randn(shape, generator=g).to(dtype).cuda()
+            got = DP.get_complete_tensor(shard, dim=dim)
+            with config.patch({"cp.peer_gather": False}):
+                want = DP.get_complete_tensor(shard, dim=dim)
+            ok = ok and got.shape == want.shape and torch.equal(got, want)
+            # and against the shards themselves
+            parts = [torch.randn(shape, generator=torch.Generator().manual_seed(r * 100 + rep)).to(dtype) for r in range(world)]
+            ok = ok and torch.equal(got.cpu(), torch.cat(parts, dim=dim))
+    torch.cuda.synchronize()
+    pa.check_device_status()
+    if rank == 0:
+        ret.put(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_get_complete_tensor_as_peer_stores_on_real_peers():
+    """The gather at the exit of a parallelised forward (src/para_attn/primitives.py:139-148) through
+    peer stores: identical to the NCCL all_gather form and to the concatenated shards."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    world = 2
+    procs = [ctx.Process(target=_gather_worker, args=(r, world, 29731, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    ok = ret.get(timeout=300)
+    for p in procs:
+        p.join(timeout=60)
+    assert ok

@@ -474,3 +474,16 @@ def test_parallel_cache_decision_matches_the_oracle_over_gloo():
         p.join(timeout=60)
     assert all(g == w for g, w in out), out
     assert {w for _, w in out} == {True, False}, "the cases must cover both outcomes"
+
+
+def test_peer_gather_block_plan():
+    """A shard is copied as whole rows of 256 or 128 bytes, one block per index of the dims in
+    front of the gather dim; shapes without whole rows are left to the collective library."""
+    from paraattention_b200._peer_gather import plan_blocks
+
+    assert plan_blocks((1, 576, 64), -2, 2) == (1, 288, 128)      # FLUX-shaped output shard on 8 ranks
+    assert plan_blocks((2, 576, 64), 1, 2) == (2, 288, 128)       # one block per batch element
+    assert plan_blocks((1, 4095, 64), 1, 2) == (1, 4095, 64)      # 128-byte rows when 256 do not divide
+    assert plan_blocks((1, 14850, 64), 1, 4) == (1, 14850, 128)   # fp32: twice the 16-bit units
+    assert plan_blocks((4, 64, 8, 16), 0, 2) == (1, 256, 128)     # gather along dim 0: one block
+    assert plan_blocks((2, 7, 3), 1, 2) is None
