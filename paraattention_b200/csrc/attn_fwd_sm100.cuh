@@ -11,8 +11,15 @@
 // TMEM columns (512 allocated): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512) for
 // head_dim 128 (O0 [256,320) O1 [320,384) for head_dim 64);
 // P_t (bf16/f16) overwrites S_t in place: the probabilities of key columns [32c, 32c+32) are
-// packed into S columns [16c, 16c+16), which are consumed by then, and P is the TMEM A operand
-// of P V. While the softmax warps of one tile work, the tensor core runs the other tile's GEMMs.
+// packed into consumed S columns of the same half of the tile ([64*(c/2) + 16*(c%2), +16)),
+// and P is the TMEM A operand of P V.
+//
+// Every query tile is run as two half-tiles in the key dimension (key columns 0-63 and 64-127
+// of each key/value tile), each with its own chain  Q K^T (N = 64) -> softmax -> P V -> next
+// Q K^T. A softmax thread alternates between the halves; while it works on one, the tensor core
+// runs the other half's P V and next Q K^T (and the other tile's), so MMA latency and the
+// hand-overs in both directions are hidden instead of waited for. The price is the N = 64
+// Q K^T, which runs at 48 instead of 32 cycles per MMA (shared-memory operand fetch).
 //
 // What bounds this kernel is each tile's chain softmax -> P V -> next Q K^T -> softmax, so the
 // softmax is arranged to keep that chain short:
@@ -132,7 +139,7 @@ struct AttnSmemCtl {
     uint64_t q_full;
     uint64_t k_full[kStages], k_empty[kStages];
     uint64_t v_full[kStages], v_empty[kStages];
-    uint64_t s_full[2];           // Q K^T of a query tile is in TMEM
+    uint64_t s_full[2][2];        // Q K^T of a query tile is in TMEM, per half of the key columns
     uint64_t p_full[2][kPieces];  // a piece of P of a query tile is in TMEM (128 arrivals)
     uint64_t o_done[2][kPieces];  // P V of a piece (and every MMA issued before it) is done
     uint64_t teardown;
@@ -260,7 +267,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_init(smem_u32(&ctl->v_empty[s]), 1);
         }
         for (int t = 0; t < 2; ++t) {
-            mbar_init(smem_u32(&ctl->s_full[t]), 1);
+            mbar_init(smem_u32(&ctl->s_full[t][0]), 1);
+            mbar_init(smem_u32(&ctl->s_full[t][1]), 1);
             for (int c = 0; c < kPieces; ++c) {
                 mbar_init(smem_u32(&ctl->p_full[t][c]), kTileM);
                 mbar_init(smem_u32(&ctl->o_done[t][c]), 1);
@@ -435,7 +443,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // the loop alone (a divergent region) needs 55 to 75 and falls behind the tensor core.
         // The k-step loops are unrolled and every descriptor is a base plus a constant.
         if (n_tiles > 0) {
-            constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN);
+            constexpr uint32_t idesc_qk = make_idesc_f16(kBF16, false, kTileM, kTileN / 2);
             constexpr uint32_t idesc_pv = make_idesc_f16(kBF16, true, kTileM, kD);
             const uint32_t leader = elect_one() ? 1u : 0u;
             const bool stamper = (lane == 0);
@@ -451,10 +459,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t lo_q = static_cast<uint32_t>(dq0);
             const uint32_t lo_k = static_cast<uint32_t>(smem_desc_sw128(sK, 16, 1024));
             const uint32_t lo_v = static_cast<uint32_t>(dv0);
-            auto issue_qk = [&](int t, int st) {
+            // Q K^T of one half of a key/value tile's rows (N = 64): key rows [64*half, 64*half+64)
+            // sit 8 KB into the tile's shared-memory slot; S columns [64*half, 64*half+64).
+            auto issue_qk_half = [&](int t, int st, int half) {
                 const uint32_t a0 = lo_q + ((t * kTileBytes) >> 4);
-                const uint32_t b0 = lo_k + ((st * kTileBytes) >> 4);
-                const uint32_t d = tmem + kColS0 + t * kTileN;
+                const uint32_t b0 = lo_k + ((st * kTileBytes + half * 64 * 128) >> 4);
+                const uint32_t d = tmem + kColS0 + t * kTileN + half * (kTileN / 2);
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
                     const uint32_t off = ((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4;
@@ -462,7 +472,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 }
             };
             // P V for key rows [32*piece, 32*piece+32) of the tile: two k-steps of 16 keys. The
-            // piece's probabilities sit at S columns [16*piece, 16*piece+16), 8 columns per k-step.
+            // piece's probabilities sit in its half of the S columns, at [64*(piece/2) +
+            // 16*(piece%2), +16), 8 columns per k-step.
             auto issue_pv_piece = [&](int t, int st, int piece, bool acc) {
                 const uint32_t b0 = lo_v + ((st * kTileBytes) >> 4);
                 const uint32_t a0 = tmem + kColS0 + t * kTileN;
@@ -472,7 +483,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     const int ks = piece * 2 + k2;
                     const uint32_t b = b0 + ((ks * 16 * 128) >> 4);
                     const uint32_t accum = (acc || ks > 0) ? 1u : 0u;
-                    tc_mma_ts_elect(d, a0 + ks * 8, b, hi_v, idesc_pv, accum, leader);
+                    tc_mma_ts_elect(d, a0 + (piece >> 1) * (kTileN / 2) + (ks & 3) * 8, b, hi_v, idesc_pv, accum, leader);
                 }
             };
 
@@ -483,10 +494,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
                 tc_fence_after();
-                issue_qk(0, 0);
-                tc_commit_elect(smem_u32(&ctl->s_full[0]), leader);
-                issue_qk(1, 0);
-                tc_commit_elect(smem_u32(&ctl->s_full[1]), leader);
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+#pragma unroll
+                    for (int t = 0; t < 2; ++t) {
+                        issue_qk_half(t, 0, half);
+                        tc_commit_elect(smem_u32(&ctl->s_full[t][half]), leader);
+                    }
                 tc_commit_elect(smem_u32(&ctl->k_empty[0]), leader);
             }
             for (int j = 0; j < n_tiles && ok; ++j) {
@@ -507,31 +521,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 // wait gives up in some lanes only)
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
+                // Each query tile is two independent half-tiles in the key dimension, each with its
+                // own chain softmax -> P V -> next Q K^T: while the softmax works on one half, the
+                // tensor core does the other half's P V and next Q K^T, so neither the MMA latency
+                // nor the hand-overs are ever waited for. (The N = 64 Q K^T runs at 48 instead of
+                // 32 cycles per MMA - shared-memory operand fetch - which this overlap pays for.)
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    dbg_stamp(p, 2, j, t * 4 + 0, stamper);
+                for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                    for (int c = 0; c < kPieces; ++c) {
-                        ok = mbar_wait(smem_u32(&ctl->p_full[t][c]), j & 1, s_abort, p.status, pipe_limit,
-                                       PA_DEV_TIMEOUT_PIPE);
-                        ok = __all_sync(0xffffffffu, ok);
+                    for (int t = 0; t < 2; ++t) {
+                        dbg_stamp(p, 2, j, (half * 2 + t) * 2 + 0, stamper);
+#pragma unroll
+                        for (int c = 2 * half; c < 2 * half + 2; ++c) {
+                            ok = mbar_wait(smem_u32(&ctl->p_full[t][c]), j & 1, s_abort, p.status, pipe_limit,
+                                           PA_DEV_TIMEOUT_PIPE);
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (!ok) break;
+                            tc_fence_after();
+                            issue_pv_piece(t, st, c, j > 0);
+                            // one barrier per piece (one phase per tile each): a softmax warp that has to
+                            // rescale O in the middle of a tile waits for the last piece issued so far
+                            tc_commit_elect(smem_u32(&ctl->o_done[t][c]), leader);
+                        }
                         if (!ok) break;
-                        if (c == 0) dbg_stamp(p, 2, j, t * 4 + 1, stamper);
-                        tc_fence_after();
-                        issue_pv_piece(t, st, c, j > 0);
-                        // one barrier per piece (one phase per tile each): a softmax warp that has to
-                        // rescale O in the middle of a tile waits for the last piece issued so far
-                        tc_commit_elect(smem_u32(&ctl->o_done[t][c]), leader);
+                        if (half == 1 && t == 1) tc_commit_elect(smem_u32(&ctl->v_empty[st]), leader);
+                        if (more) {
+                            issue_qk_half(t, stn, half);
+                            tc_commit_elect(smem_u32(&ctl->s_full[t][half]), leader);
+                            if (half == 1 && t == 1) tc_commit_elect(smem_u32(&ctl->k_empty[stn]), leader);
+                        }
+                        dbg_stamp(p, 2, j, (half * 2 + t) * 2 + 1, stamper);
                     }
                     if (!ok) break;
-                    if (t == 1) tc_commit_elect(smem_u32(&ctl->v_empty[st]), leader);
-                    dbg_stamp(p, 2, j, t * 4 + 2, stamper);
-                    if (more) {
-                        issue_qk(t, stn);
-                        tc_commit_elect(smem_u32(&ctl->s_full[t]), leader);
-                        if (t == 1) tc_commit_elect(smem_u32(&ctl->k_empty[stn]), leader);
-                    }
-                    dbg_stamp(p, 2, j, t * 4 + 3, stamper);
                 }
             }
             if (!ok) {
@@ -551,7 +572,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t tS = tmem + lane_base + kColS0 + t * kTileN;  // my row's 128 logits
         const uint32_t tO = tmem + lane_base + kColO0 + t * kD;      // my row of the output
-        const uint32_t bs = smem_u32(&ctl->s_full[t]);
         const float sl = p.scale_log2;
         const bool stamper = (quarter == 0 && lane == 0);
 
@@ -559,6 +579,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         float l_sum = 0.f;
         bool ok = true;
         int j = 0;
+        uint32_t buf[2][32];  // the logits of the piece at hand and of the next one
+        bool pre = false;     // the load of the next piece has been issued
+        int pending = -1;     // piece whose probabilities are stored but not handed over yet
         const long long q_here = kCausal ? p.q_pos[qc] + row0 + t * kTileM + row_in_tile : 0;  // my row's global position
         for (int ci = 0; ci < p.n_kv_chunks; ++ci) {
             int c_kv = p.kv_first + ci;
@@ -581,21 +604,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     if (exist > 64) kw[1] = __ldg(w + 1);
                 }
                 const bool plain = (valid == kTileN) && (p.key_bits == nullptr);
-                dbg_stamp(p, t, j, 0, stamper);
-                // A wait that gives up does not leave the loop: once the abort word is set no wait
-                // blocks any more, and the arrivals below keep the other roles moving.
-                ok = mbar_wait(bs, j & 1, s_abort, p.status, pipe_limit, PA_DEV_TIMEOUT_PIPE) && ok;
-                dbg_stamp(p, t, j, 1, stamper);
-                tc_fence_after();
                 const bool plain_warp = __all_sync(0xffffffffu, plain);
-                uint32_t buf[2][32];
-                tmem_ld32(tS, buf[0]);
+                // The tile is worked on as two halves of its key columns (pieces 0,1 and 2,3), each as
+                // soon as its Q K^T has landed; while this thread is busy with one half the tensor
+                // core runs the other half's P V and next Q K^T. The pieces form one rolling
+                // pipeline across halves and tiles: while piece c is exponentiated the load of
+                // the next piece is in flight - if that piece opens a new half, only when its
+                // Q K^T is already there (one non-blocking look at the barrier), which it is
+                // whenever the tensor core is ahead - and the hand-over of a half's first piece is
+                // issued behind the second piece's exponentials, when its TMEM store has long landed.
 #pragma unroll
                 for (int c = 0; c < kPieces; ++c) {
-                    uint32_t(&sc)[32] = buf[c & 1];
+                    const int half = c >> 1, i = c & 1;
+                    uint32_t(&sc)[32] = buf[i];
+                    if (!pre) {
+                        if (pending >= 0) {  // never block with a hand-over outstanding
+                            tc_wait_st();
+                            tc_fence_before();
+                            mbar_arrive(smem_u32(&ctl->p_full[t][pending]));
+                            pending = -1;
+                        }
+                        if (i == 0) {
+                            dbg_stamp(p, t, j, half * 4 + 0, stamper);
+                            // A wait that gives up does not leave the loop: once the abort word is set
+                            // no wait blocks any more, and the arrivals keep the other roles moving.
+                            ok = mbar_wait(smem_u32(&ctl->s_full[t][half]), j & 1, s_abort, p.status, pipe_limit,
+                                           PA_DEV_TIMEOUT_PIPE) && ok;
+                            tc_fence_after();
+                            dbg_stamp(p, t, j, half * 4 + 1, stamper);
+                        }
+                        tmem_ld32(tS + c * kPieceCols, sc);
+                    }
                     tc_wait_ld();
                     tmem_ld_fence(sc);
-                    if (c + 1 < kPieces) tmem_ld32(tS + (c + 1) * kPieceCols, buf[(c + 1) & 1]);
+                    // the next piece: same half - its logits are there; first piece of the other half or
+                    // of the next tile - only if its Q K^T has already been committed
+                    pre = false;
+                    if (i == 0) {
+                        pre = true;
+                    } else if (c == 1) {
+                        pre = __all_sync(0xffffffffu, mbar_try_wait(smem_u32(&ctl->s_full[t][1]), j & 1));
+                    } else if (j + 1 < n_tiles) {
+                        pre = __all_sync(0xffffffffu, mbar_try_wait(smem_u32(&ctl->s_full[t][0]), (j + 1) & 1));
+                    }
+                    if (pre) {
+                        if (i == 1) tc_fence_after();
+                        tmem_ld32(tS + ((c + 1) & 3) * kPieceCols, buf[i ^ 1]);
+                    }
                     uint32_t live = 0xffffffffu;
                     uint32_t pk[16];
                     float ls, mx;
@@ -605,42 +660,55 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                     } else {
                         const int v = valid - c * kPieceCols;
                         live = (v >= 32) ? 0xffffffffu : (v <= 0 ? 0u : ((1u << v) - 1u));
-                        live &= static_cast<uint32_t>(kw[c >> 1] >> ((c & 1) * 32));
+                        live &= static_cast<uint32_t>(kw[half] >> (i * 32));
                         softmax_chunk<kBF16, true>(sc, live, sl, neg, pk, ls, mx);
                     }
-                    // The previous piece is handed over only now, behind this piece's exponentials
-                    // in program order: its store has long landed, so the wait costs nothing and
-                    // the special-function unit is never left idle for a round trip to TMEM.
-                    if (c > 0) {
+                    if (pending >= 0) {  // the previous piece, behind this piece's exponentials
                         tc_wait_st();
                         tc_fence_before();
-                        mbar_arrive(smem_u32(&ctl->p_full[t][c - 1]));
-                        dbg_stamp(p, t, j, 1 + c, stamper);
+                        mbar_arrive(smem_u32(&ctl->p_full[t][pending]));
+                        pending = -1;
                     }
                     // (m_ref = mx = -inf: NaN > threshold is false, the row stays empty)
                     const bool grow = (mx - m_ref) * sl > kRescaleThreshold;
+                    // P of key columns [32c, 32c+32) goes over consumed S columns of its half
+                    const uint32_t tP = tS + half * (kTileN / 2) + i * (kPieceCols / 2);
                     if (__any_sync(0xffffffffu, grow)) {
+                        if (pre) {  // no load may be in flight across the call
+                            tc_wait_ld();
+                            tmem_ld_fence(buf[i ^ 1]);
+                        }
                         // every P V handed over so far must have been added to O before O is
                         // rescaled: the last one is waited for (MMAs complete in order)
                         const uint32_t bo = (c > 0) ? smem_u32(&ctl->o_done[t][c - 1])
                                                     : smem_u32(&ctl->o_done[t][kPieces - 1]);
                         const uint32_t par = (c > 0) ? (j & 1) : ((j - 1) & 1);
                         const float2 r = softmax_piece_regrow<kBF16, kD>(
-                            tS + c * kPieceCols, tS + c * (kPieceCols / 2), tO, live, sl, mx, m_ref, l_sum, j > 0 || c > 0,
-                            bo, par, s_abort, p.status, pipe_limit);
+                            tS + c * kPieceCols, tP, tO, live, sl, mx, m_ref, l_sum, j > 0 || c > 0, bo, par, s_abort,
+                            p.status, pipe_limit);
                         m_ref = r.x;
                         l_sum = r.y;
                     } else {
                         l_sum += ls;
-                        // P of key columns [32c, 32c+32) over S columns [16c, 16c+16): consumed by now
-                        tmem_st16(tS + c * (kPieceCols / 2), pk);
+                        tmem_st16(tP, pk);
                     }
+                    // (a half's last piece is handed over at once: its P V and the half's next Q K^T
+                    // have only the time this thread spends on the other half)
+                    if (i == 0) {
+                        pending = c;
+                    } else {
+                        tc_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(smem_u32(&ctl->p_full[t][c]));
+                    }
+                    if (i == 1) dbg_stamp(p, t, j, half * 4 + 3, stamper);
                 }
-                tc_wait_st();
-                tc_fence_before();
-                mbar_arrive(smem_u32(&ctl->p_full[t][kPieces - 1]));
-                dbg_stamp(p, t, j, 1 + kPieces, stamper);
             }
+        }
+        if (pending >= 0) {
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->p_full[t][pending]));
         }
         // (a CTA whose queries see no key at all writes zeros and an LSE of -inf)
         const bool empty = (n_tiles == 0);

@@ -65,6 +65,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // when `limit_ns` ran out; in the latter case it publishes `code` to the abort word and to
 // the kernel's global status word (first writer wins) so that every other wait in the grid
 // gives up quickly too.
+// (A try_wait with a suspend-time hint instead of the plain one was measured: no gain.)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort,
                                           int* g_status, uint64_t limit_ns, int code) {
     if (mbar_try_wait(bar, parity)) return true;
