@@ -334,6 +334,11 @@ def run_ours(args):
         # the attention kernel (the exchange rides inside it); Ulysses meshes add the one-warp
         # wait for the output tiles and the hand-out copy; causal runs one more one-warp wait
         launches_per_step = 1 + (2 if U > 1 else 0) + (1 if causal else 0)
+    # a launch whose last wave is split (the library decides per shape) is two launches
+    split = split_plan(torch, dev, ((S_pad // world + 255) // 256) * (H // U) * U,
+                       ((S_pad // world + 127) // 128) * world, causal)
+    if split["k"] > 1 and split["from"] > 0:
+        launches_per_step += 1
 
     def sync_all():
         torch.cuda.synchronize(dev)
@@ -461,7 +466,8 @@ def run_ours(args):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": workload_name(H, S), "mesh": f"{U}x{R} (ulysses x ring)", "per_gpu_tflops": per_gpu_tflops,
-                   "l2": "256 MB flush between timed iterations", "timing": "CUDA events per step, max over ranks"},
+                   "l2": "256 MB flush between timed iterations", "timing": "CUDA events per step, max over ranks",
+                   "split_last_wave": split},
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "parity": parity,
         "gpu_launches": launches_per_step * args.steps,
     }
@@ -490,6 +496,20 @@ TRAFFIC_BYTES_PER_LAUNCH = {
 # ------------------------------------------------------------------------------------------
 # comparator: the reference's GPU path (library SDPA + NCCL) on the same GPUs
 # ------------------------------------------------------------------------------------------
+def split_plan(torch, dev, units, kv_tiles, causal):
+    """What the attention launch of this shape does with its last wave: {"from", "k", "units"}
+    (k = 1: one CTA per work unit everywhere)."""
+    import ctypes as C
+    from paraattention_b200 import _lib as L, config
+
+    lib = L.load()
+    ws = int(lib.pa_attn_workspace_bytes()) if config.attention.split_last_wave else 0
+    f, k = C.c_int32(units), C.c_int32(1)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    L.check(lib.pa_attn_split_plan(units, sms, kv_tiles, VARIANT["D"], int(causal), ws, C.byref(f), C.byref(k)))
+    return {"units": units, "from": f.value, "k": k.value}
+
+
 def run_reference_gpu(args, c):
     """Times what the reference runs on GPUs for this step: at world size 1 PyTorch's SDPA; on a
     mesh the Ulysses all-to-alls (src/para_attn/para_attn_interface.py:52-119) around PyTorch's

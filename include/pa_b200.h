@@ -79,7 +79,25 @@ typedef struct pa_attn_args {
      * _attention_forward_sparse_kv does with index_select (src/para_attn/ops/__init__.py:248-299).
      * A query row without any visible key comes out as zeros with an LSE of -inf. */
     const uint64_t* key_bits;
+    /* Optional scratch (NULL: none), 256-byte aligned device memory of workspace_bytes bytes that
+     * calls running at the same time must not share. With it, a non-causal launch whose last wave
+     * of CTAs would leave most SMs idle gives each work unit of that wave to several CTAs that
+     * split the keys among them and combine their partial results before the output is written
+     * (same result up to fp32 summation order). pa_attn_workspace_bytes() is a size that covers
+     * every shape; with less, fewer CTAs share a unit, or none. */
+    void* workspace;
+    int64_t workspace_bytes;
 } pa_attn_args;
+
+int64_t pa_attn_workspace_bytes(void);
+
+/* What a launch with `units` work units (pairs of 128-row query tiles x heads x batch x query
+ * chunks) and kv_tiles key/value tiles of 128 rows per unit does with a workspace of that size on
+ * a device with sm_count SMs: units [0, *split_from) are computed by one CTA each, every later
+ * unit by *split_k CTAs in a second launch (*split_k = 1, *split_from = units: one launch,
+ * nothing split). Needs no device. */
+int pa_attn_split_plan(int64_t units, int32_t sm_count, int64_t kv_tiles, int32_t head_dim, int32_t is_causal,
+                       int64_t workspace_bytes, int32_t* split_from, int32_t* split_k);
 
 int pa_attn_fwd(const pa_attn_args* args, void* stream);
 
@@ -152,6 +170,9 @@ typedef struct pa_cp_attn_args {
      * from pa_pack_key_mask. Lifts the reference's "no mask with ring attention" limit
      * (src/para_attn/para_attn_interface.py:228). */
     const uint64_t* key_bits;
+    /* Optional scratch, as in pa_attn_args (local device memory, never a peer's). */
+    void* workspace;
+    int64_t workspace_bytes;
 } pa_cp_attn_args;
 
 int pa_cp_attn_fwd(const pa_cp_attn_args* args, void* stream);

@@ -39,6 +39,7 @@ class AttnArgs(C.Structure):
         ("o_stride", C.c_int64 * 3),
         ("status", C.c_void_p), ("wait_limit_ns", C.c_uint64),
         ("key_bits", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -63,6 +64,7 @@ class CpAttnArgs(C.Structure):
         ("is_causal", C.c_int32), ("pad_", C.c_int32),
         ("q_pos", C.c_int64 * PA_MAX_CHUNKS), ("kv_pos", C.c_int64 * PA_MAX_CHUNKS),
         ("key_bits", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -117,6 +119,11 @@ def load() -> C.CDLL:
     lib.pa_last_error.restype = C.c_char_p
     lib.pa_last_error.argtypes = []
     lib.pa_version.restype = C.c_int
+    lib.pa_attn_workspace_bytes.restype = C.c_int64
+    lib.pa_attn_workspace_bytes.argtypes = []
+    lib.pa_attn_split_plan.restype = C.c_int
+    lib.pa_attn_split_plan.argtypes = [C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int64,
+                                       C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.pa_attn_fwd.restype = C.c_int
     lib.pa_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
     lib.pa_qkv_prep.restype = C.c_int

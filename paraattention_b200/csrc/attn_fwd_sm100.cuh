@@ -120,6 +120,16 @@ struct AttnParams {
     // row i of that chunk may be attended to; strides in 64-bit words
     const unsigned long long* key_bits;
     long long kb_sb, kb_sc;
+    // Split of the last, under-filled wave, a launch of its own (the kSplit instantiation): work
+    // units from `split_from` on are each computed by `split_k` consecutive CTAs, every one over
+    // its own share of the key/value tiles. part_o [unit][share][head_dim / 4][256 rows][4] and
+    // part_ml [unit][share][256 rows] (reference, row sum) hold the shares' results, part_cnt
+    // [unit][9] counts finished warps (8) and finished CTAs (zeroed by the host before the launch).
+    int split_from, split_k;
+    int unit_base;  // kSplit launches: work unit of the first CTA
+    float* part_o;
+    float2* part_ml;
+    unsigned int* part_cnt;
 #if PA_TIMELINE
     long long* dbg_t;  // clock64 stamps of CTA 0: [role 0..4][step][8]; roles: softmax 0, softmax 1, MMA issuer, TMA producer, MMA operand waits
     int dbg_steps;
@@ -145,6 +155,10 @@ struct AttnSmemCtl {
     uint64_t teardown;
     uint32_t tmem_base;
     int abort;
+    // kSplit launches: which unit of the split wave, which share of its tiles, first tile. Kept
+    // here (every thread writes the same values and reads them back where it needs them) rather
+    // than in registers across the main loop.
+    int split_unit, share, j_begin;
 };
 
 constexpr int kAttnCtlBytes = 512;
@@ -228,7 +242,105 @@ __device__ __noinline__ float2 softmax_piece_regrow(uint32_t tS_piece, uint32_t 
     return make_float2(m_new, l_sum * alpha + ls);
 }
 
-template <bool kBF16, bool kCausal, int kD>
+// Epilogue of a CTA that computed one share of a split work unit (all 32 lanes of a softmax warp
+// call; one thread per query row). The warp stores its rows' unnormalised output, reference and
+// row sum as this share's result and counts itself on the unit's counter for this warp slot;
+// the warp that finds all the other shares already counted combines them with its own -
+// out = sum_i 2^((m_i - m) * sl) O_i / sum_i 2^((m_i - m) * sl) l_i - and writes the final rows
+// and their LSE. Nobody waits: the last warp to arrive does the work, whichever share it is.
+// Returns nothing; rows beyond the query chunk (`in_range` false) are not written.
+template <bool kBF16, int kD>
+__device__ __noinline__ void split_epilogue(uint32_t tO, float m_ref, float l_sum, float sl, float scale, int lane,
+                                            int slot_row, int share, int split_k, float* part_o, float2* part_ml,
+                                            unsigned int* cnt, uint16_t* orow, float* lse_row, bool in_range) {
+    // slot_row: this row's index within the unit's 256 rows. A share's output is stored as
+    // [head_dim / 4][256 rows] groups of four columns, so that the 32 rows of a warp store and
+    // load 512 contiguous bytes at a time.
+    constexpr int kGroups = kD / 4;
+    uint4* mine_o = reinterpret_cast<uint4*>(part_o) + static_cast<size_t>(share) * kGroups * (2 * kTileM) + slot_row;
+#pragma unroll
+    for (int b = 0; b < kD / 32; ++b) {
+        uint32_t o[32];
+        tmem_ld32(tO + b * 32, o);
+        tc_wait_ld();
+        tmem_ld_fence(o);
+#pragma unroll
+        for (int v4 = 0; v4 < 8; ++v4)
+            __stcg(mine_o + static_cast<size_t>(b * 8 + v4) * (2 * kTileM),
+                   make_uint4(o[4 * v4], o[4 * v4 + 1], o[4 * v4 + 2], o[4 * v4 + 3]));
+    }
+    __stcg(part_ml + static_cast<size_t>(share) * (2 * kTileM) + slot_row, make_float2(m_ref, l_sum));
+    __threadfence();
+    __syncwarp();
+    unsigned int before = 0;
+    if (lane == 0) before = atomicAdd(cnt, 1u);
+    before = __shfl_sync(0xffffffffu, before, 0);
+    if (before + 1u != static_cast<unsigned int>(split_k)) return;
+    __threadfence();
+
+    float m_tot = m_ref;
+    for (int i = 0; i < split_k; ++i) {
+        if (i == share) continue;
+        m_tot = fmaxf(m_tot, __ldcg(part_ml + static_cast<size_t>(i) * (2 * kTileM) + slot_row).x);
+    }
+    // (a share whose rows saw no key has m = -inf and weighs nothing)
+    auto weight = [&](float m) -> float { return (m == -INFINITY) ? 0.0f : ex2_approx((m - m_tot) * sl); };
+    float l_tot = 0.0f;
+    for (int i = 0; i < split_k; ++i) {
+        const float2 ml = (i == share) ? make_float2(m_ref, l_sum)
+                                       : __ldcg(part_ml + static_cast<size_t>(i) * (2 * kTileM) + slot_row);
+        l_tot += ml.y * weight(ml.x);
+    }
+    const float inv = (l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
+    // (the shares are added in index order, this warp's own at its place, whichever share it
+    // is: the result does not depend on who arrives last)
+#pragma unroll 1
+    for (int b = 0; b < kD / 32; ++b) {
+        float acc[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+        for (int i = 0; i < split_k; ++i) {
+            if (i == share) {
+                const float w = weight(m_ref) * inv;
+                uint32_t o[32];
+                tmem_ld32(tO + b * 32, o);
+                tc_wait_ld();
+                tmem_ld_fence(o);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) acc[c] = fmaf(__uint_as_float(o[c]), w, acc[c]);
+                continue;
+            }
+            const float w = weight(__ldcg(part_ml + static_cast<size_t>(i) * (2 * kTileM) + slot_row).x) * inv;
+            const uint4* src = reinterpret_cast<const uint4*>(part_o) +
+                               (static_cast<size_t>(i) * kGroups + b * 8) * (2 * kTileM) + slot_row;
+#pragma unroll
+            for (int v4 = 0; v4 < 8; ++v4) {
+                const uint4 x = __ldcg(src + static_cast<size_t>(v4) * (2 * kTileM));
+                acc[4 * v4 + 0] = fmaf(__uint_as_float(x.x), w, acc[4 * v4 + 0]);
+                acc[4 * v4 + 1] = fmaf(__uint_as_float(x.y), w, acc[4 * v4 + 1]);
+                acc[4 * v4 + 2] = fmaf(__uint_as_float(x.z), w, acc[4 * v4 + 2]);
+                acc[4 * v4 + 3] = fmaf(__uint_as_float(x.w), w, acc[4 * v4 + 3]);
+            }
+        }
+        if (in_range) {
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+                uint4 w4;
+                uint32_t* wp = reinterpret_cast<uint32_t*>(&w4);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    wp[i] = kBF16 ? pack_bf16x2(acc[v4 * 8 + 2 * i], acc[v4 * 8 + 2 * i + 1])
+                                  : pack_f16x2(acc[v4 * 8 + 2 * i], acc[v4 * 8 + 2 * i + 1]);
+                *reinterpret_cast<uint4*>(orow + b * 32 + v4 * 8) = w4;
+            }
+        }
+    }
+    if (in_range && lse_row != nullptr) *lse_row = (l_tot > 0.0f) ? m_tot * scale + __logf(l_tot) : -INFINITY;
+}
+
+// kSplit: the launch that computes the work units of a split last wave (see AttnParams); the
+// instantiation without it carries none of that code.
+template <bool kBF16, bool kCausal, int kD, bool kSplit = false>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_ql,
@@ -305,6 +417,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         unit -= push.n_push_ctas;
         if (unit < 0) unit += gridDim.x;
     }
+    // (a unit of the split last wave belongs to split_k consecutive CTAs)
+    volatile int* s_split = &ctl->split_unit;  // [0] unit of the split wave, [1] share, [2] first tile
+    if (kSplit) {
+        int split_unit = -1, share = 0;  // (units before split_from are computed whole)
+        unit += p.unit_base;
+        if (unit >= p.split_from) {
+            split_unit = (unit - p.split_from) / p.split_k;
+            share = (unit - p.split_from) - split_unit * p.split_k;
+            unit = p.split_from + split_unit;
+        }
+        s_split[0] = split_unit;
+        s_split[1] = share;
+    }
     int pair = unit % pairs_per_chunk;
     unit /= pairs_per_chunk;
     // the late query tiles of a causal run see the most keys: schedule them first
@@ -329,6 +454,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     };
     int n_tiles = 0;
     for (int c = 0; c < p.n_kv_chunks; ++c) n_tiles += tiles_in_chunk(c);
+    // This CTA's part of the unit's tile list (all of it unless the unit is split): tiles
+    // [j_begin, j_begin + n_tiles) in the order the chunks are walked.
+    if (kSplit) {
+        const int share = s_split[1];
+        const int k = (s_split[0] >= 0) ? p.split_k : 1;
+        const int j_begin = static_cast<int>(static_cast<long long>(n_tiles) * share / k);
+        n_tiles = static_cast<int>(static_cast<long long>(n_tiles) * (share + 1) / k) - j_begin;
+        s_split[2] = j_begin;
+    }
     const uint64_t pipe_limit = p.wait_ns + 1000000000ull;
 
     // Fused exchange: the leading CTAs of the grid (always resident in the first wave, and
@@ -373,11 +507,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                     row0 + t * kTileM, hq, bidx, cq);
             }
             int j = 0;
+            int walked = 0;  // tiles of the chunks before this one
             for (int ci = 0; ci < p.n_kv_chunks && ok; ++ci) {
                 int c = p.kv_first + ci;
                 if (c >= p.n_kv_chunks) c -= p.n_kv_chunks;
                 const int tiles_c = tiles_in_chunk(c);
-                if (tiles_c == 0) continue;
+                const int t_lo = kSplit ? max(0, s_split[2] - walked) : 0;
+                const int t_hi = kSplit ? min(tiles_c, s_split[2] + n_tiles - walked) : tiles_c;
+                if (kSplit) walked += tiles_c;
+                if (t_lo >= t_hi) continue;  // (a chunk none of whose tiles are mine is not waited for)
                 const bool kv_in_place = (c == p.kv_local_chunk);
                 if (!kv_in_place && p.kv_flag[c] != nullptr) {
                     ok = flag_wait_ge(p.kv_flag[c], p.flag_expect, s_abort, p.status, p.wait_ns,
@@ -389,7 +527,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const CUtensorMap* mv = kv_in_place ? &tm_vl : &tm_v;
                 const int hk = kv_in_place ? head + p.local_head0 : head;
                 const int ck = kv_in_place ? 0 : c;
-                for (int t = 0; t < tiles_c; ++t, ++j) {
+                for (int t = t_lo; t < t_hi; ++t, ++j) {
                     const int st = j & 1;
                     const uint32_t ph = (j >> 1) & 1;
                     const uint32_t bk = smem_u32(&ctl->k_full[st]);
@@ -583,11 +721,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         bool pre = false;     // the load of the next piece has been issued
         int pending = -1;     // piece whose probabilities are stored but not handed over yet
         const long long q_here = kCausal ? p.q_pos[qc] + row0 + t * kTileM + row_in_tile : 0;  // my row's global position
+        int walked = 0;
         for (int ci = 0; ci < p.n_kv_chunks; ++ci) {
             int c_kv = p.kv_first + ci;
             if (c_kv >= p.n_kv_chunks) c_kv -= p.n_kv_chunks;
             const int tiles_c = tiles_in_chunk(c_kv);
-            for (int tk = 0; tk < tiles_c; ++tk, ++j) {
+            const int t_lo = kSplit ? max(0, s_split[2] - walked) : 0;
+            const int t_hi = kSplit ? min(tiles_c, s_split[2] + n_tiles - walked) : tiles_c;
+            if (kSplit) walked += tiles_c;
+            for (int tk = t_lo; tk < t_hi; ++tk, ++j) {
                 // which of the tile's 128 key columns count for my row: the key mask words (the
                 // same for the whole warp), cut at the ragged end of the chunk and at the causal
                 // diagonal
@@ -724,6 +866,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             uint16_t* orow = reinterpret_cast<uint16_t*>(p.out[qc]) +
                              (static_cast<long long>(bidx) * p.o_sb + static_cast<long long>(head) * p.o_sh +
                               static_cast<long long>(row) * p.o_ss);
+            if (kSplit && s_split[0] >= 0) {
+                const int split_unit = s_split[0], share = s_split[1];
+                const size_t base = static_cast<size_t>(split_unit) * p.split_k * (2 * kTileM);
+                float* lse_row = (p.lse[qc] == nullptr) ? nullptr
+                                                        : p.lse[qc] + static_cast<long long>(bidx) * p.l_sb +
+                                                              static_cast<long long>(head) * p.l_sh + row;
+                split_epilogue<kBF16, kD>(tO, empty ? -INFINITY : m_ref, empty ? 0.0f : l_sum, sl, p.scale, lane,
+                                          t * kTileM + row_in_tile, share, p.split_k, p.part_o + base * kD,
+                                          p.part_ml + base, p.part_cnt + split_unit * 9 + warp, orow, lse_row,
+                                          in_range);
+            } else {
 #pragma unroll
             for (int b = 0; b < kD / 32; ++b) {
                 uint32_t o[32];
@@ -753,6 +906,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 p.lse[qc][static_cast<long long>(bidx) * p.l_sb + static_cast<long long>(head) * p.l_sh + row] =
                     m_ref * p.scale + __logf(l_sum);
             }
+            }
         }
     }
 
@@ -760,9 +914,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncthreads();
     if (p.done_flag[qc] != nullptr && *s_abort == 0) {
         // every output store of this CTA is ordered before the counter update
+        // (of a split unit's CTAs the one that finishes last reports the unit: by then every
+        // share's warps have written whatever rows fell to them)
         if (threadIdx.x == 0) {
             __threadfence_system();
-            red_release_sys_add(p.done_flag[qc], 1u);
+            bool report = true;
+            if (kSplit && s_split[0] >= 0) {
+                report = (atomicAdd(p.part_cnt + s_split[0] * 9 + 8, 1u) + 1u == static_cast<unsigned int>(p.split_k));
+                if (report) __threadfence_system();
+            }
+            if (report) red_release_sys_add(p.done_flag[qc], 1u);
         }
     }
     if (warp == kMmaWarp) {

@@ -92,10 +92,10 @@ int make_map(CUtensorMap* map, const void* base, int dtype, int head_dim, int ro
     return PA_OK;
 }
 
-template <bool kBF16, bool kCausal, int kD>
+template <bool kBF16, bool kCausal, int kD, bool kSplit = false>
 int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream) {
-    auto kern = pa::attn_fwd_kernel<kBF16, kCausal, kD>;
+    auto kern = pa::attn_fwd_kernel<kBF16, kCausal, kD, kSplit>;
     static bool configured[64] = {};  // per instantiation and device
     static std::mutex mu;
     {
@@ -114,15 +114,104 @@ int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa:
     return PA_OK;
 }
 
+// One launch over all work units, or - when the last wave is split - one over the whole waves
+// and a second one (no pushers: those belong to the first wave) in which every remaining unit
+// belongs to split_k CTAs.
 template <bool kBF16>
 int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream, int head_dim) {
+    if (p.split_k > 1) {
+        int rc = PA_OK;
+        if (p.split_from > 0) {
+            pa::AttnParams whole = p;
+            whole.split_k = 1;
+            rc = launch_attn<kBF16>(maps, whole, push, p.split_from, stream, head_dim);
+            if (rc != PA_OK) return rc;
+        }
+        // (with fewer units than SMs there is no first launch, and the pushers lead this one)
+        pa::PushParams none;
+        memset(&none, 0, sizeof(none));
+        const pa::PushParams& tail_push = (p.split_from > 0) ? none : push;
+        const int tail_grid = (grid - p.split_from) * p.split_k;
+        pa::AttnParams tail = p;
+        tail.unit_base = p.split_from;
+        return head_dim == 64 ? launch_attn_inst<kBF16, false, 64, true>(maps, tail, tail_push, tail_grid, stream)
+                              : launch_attn_inst<kBF16, false, 128, true>(maps, tail, tail_push, tail_grid, stream);
+    }
     if (head_dim == 64) {
         return p.causal ? launch_attn_inst<kBF16, true, 64>(maps, p, push, grid, stream)
                         : launch_attn_inst<kBF16, false, 64>(maps, p, push, grid, stream);
     }
     return p.causal ? launch_attn_inst<kBF16, true, 128>(maps, p, push, grid, stream)
                     : launch_attn_inst<kBF16, false, 128>(maps, p, push, grid, stream);
+}
+
+// Split of the last wave. A grid of `units` equally long CTAs on `sms` SMs takes
+// ceil(units / sms) rounds although the last round may be nearly empty (384 units on 148 SMs:
+// 2.59 rounds of work in the time of 3). With a workspace the units of the last round are each
+// given to k CTAs that take 1/k of the key/value tiles and combine their results in the
+// kernel's epilogue, so that the last round costs ceil(tail * k / sms) / k of a round instead
+// of a whole one. k is the value in [2, 8] with the lowest modelled cost (every extra CTA is
+// charged 2 % of a unit for its prologue and the exchange of partial results) that leaves at
+// least 8 tiles per CTA and fits the workspace; nothing is split unless the model promises 3 %
+// of the call. Causal runs (units of unequal length, long ones first) are left alone.
+struct TailSplit {
+    int from = 0, k = 1;
+    long long grid = 0;
+    size_t cnt_bytes = 0, ml_bytes = 0, o_bytes = 0;
+};
+
+TailSplit plan_tail_split(long long units, int sms, long long kv_tiles, int head_dim, bool causal, int64_t ws_bytes) {
+    TailSplit r;
+    r.from = int(units);
+    r.grid = units;
+    if (causal || ws_bytes <= 0 || sms <= 0 || units <= 0) return r;
+    const long long tail = units % sms;
+    if (tail == 0) return r;
+    const double rounds_now = double(units / sms + 1);
+    double best = 1.0;
+    int best_k = 1;
+    for (int k = 2; k <= 8; ++k) {
+        if (kv_tiles / k < 8) break;
+        const size_t need = 256 + size_t(tail) * 9 * 4 + size_t(tail) * k * 256 * (8 + size_t(head_dim) * 4) + 512;
+        if (need > size_t(ws_bytes)) break;
+        const long long rounds = (tail * k + sms - 1) / sms;
+        const double cost = double(rounds) * (1.0 / k + 0.02);
+        if (cost < best - 1e-9) {
+            best = cost;
+            best_k = k;
+        }
+    }
+    if (best_k == 1 || (1.0 - best) / rounds_now < 0.03) return r;
+    r.k = best_k;
+    r.from = int(units - tail);
+    r.grid = (units - tail) + tail * best_k;
+    r.cnt_bytes = (size_t(tail) * 9 * 4 + 255) & ~size_t(255);
+    r.ml_bytes = (size_t(tail) * best_k * 256 * 8 + 255) & ~size_t(255);
+    r.o_bytes = size_t(tail) * best_k * 256 * size_t(head_dim) * 4;
+    return r;
+}
+
+// Fills the split fields of `p` and zeroes the counters on the stream; returns the grid size.
+int apply_tail_split(pa::AttnParams* p, long long units, long long kv_tiles, int head_dim, void* ws, int64_t ws_bytes,
+                     cudaStream_t s, long long* grid) {
+    p->split_from = int(units);
+    p->split_k = 1;
+    *grid = units;
+    if (ws == nullptr) return PA_OK;
+    if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return fail(PA_EINVAL, "workspace must be 256-byte aligned");
+    const TailSplit t = plan_tail_split(units, sm_count(), kv_tiles, head_dim, p->causal != 0, ws_bytes);
+    if (t.k == 1) return PA_OK;
+    if ((units - t.from) * t.k > 0x7fffffffLL) return PA_OK;
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    p->part_cnt = reinterpret_cast<unsigned int*>(base);
+    p->part_ml = reinterpret_cast<float2*>(base + t.cnt_bytes);
+    p->part_o = reinterpret_cast<float*>(base + t.cnt_bytes + t.ml_bytes);
+    p->split_from = t.from;
+    p->split_k = t.k;
+    cudaError_t e = cudaMemsetAsync(p->part_cnt, 0, t.cnt_bytes, s);
+    if (e != cudaSuccess) return fail(PA_ECUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return PA_OK;
 }
 
 int check_common(int head_dim, int dtype, float scale) {
@@ -195,9 +284,12 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, long long* dbg_t = nullpt
 #endif
 
     const long long pairs = (a->seq_q + 255) / 256;
-    const long long grid = pairs * a->heads * a->batch;
-    if (grid > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
+    const long long units = pairs * a->heads * a->batch;
+    if (units > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    long long grid = units;
+    rc = apply_tail_split(&p, units, (a->seq_kv + 127) / 128, a->head_dim, a->workspace, a->workspace_bytes, s, &grid);
+    if (rc != PA_OK) return rc;
     pa::PushParams push;
     memset(&push, 0, sizeof(push));
     return a->dtype == PA_BF16 ? launch_attn<true>(maps, p, push, int(grid), s, a->head_dim)
@@ -238,6 +330,18 @@ extern "C" {
 
 const char* pa_last_error(void) { return g_err; }
 int pa_version(void) { return 1; }
+
+int64_t pa_attn_workspace_bytes(void) { return int64_t(64) << 20; }
+
+int pa_attn_split_plan(int64_t units, int32_t sm_count_, int64_t kv_tiles, int32_t head_dim, int32_t is_causal,
+                       int64_t workspace_bytes, int32_t* split_from, int32_t* split_k) {
+    if (units <= 0 || sm_count_ <= 0 || kv_tiles <= 0 || (head_dim != 64 && head_dim != 128))
+        return fail(PA_EINVAL, "units, sm_count and kv_tiles must be positive, head_dim 64 or 128");
+    const TailSplit t = plan_tail_split(units, sm_count_, kv_tiles, head_dim, is_causal != 0, workspace_bytes);
+    if (split_from != nullptr) *split_from = t.from;
+    if (split_k != nullptr) *split_k = t.k;
+    return PA_OK;
+}
 
 int pa_attn_fwd(const pa_attn_args* args, void* stream) { return attn_fwd_impl(args, stream); }
 
@@ -349,20 +453,25 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     p.wait_ns = a->wait_limit_ns ? a->wait_limit_ns : 2000000000ull;
 
     const long long pairs = (a->q_rows + 255) / 256;
-    const long long grid = pairs * a->heads * a->batch * a->n_q_chunks;
-    if (grid > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
+    const long long units = pairs * a->heads * a->batch * a->n_q_chunks;
+    if (units > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    long long grid = units;
+    rc = apply_tail_split(&p, units, static_cast<long long>((a->kv_rows + 127) / 128) * a->n_kv_chunks, a->head_dim,
+                          a->workspace, a->workspace_bytes, s, &grid);
+    if (rc != PA_OK) return rc;
     pa::PushParams push;
     memset(&push, 0, sizeof(push));
     if (a->fused_push != nullptr) {
         rc = fill_push(a->fused_push, &push);
         if (rc != PA_OK) return rc;
-        // pushers must all be resident at once: never more than the grid or one wave of SMs
+        // pushers must all be resident at once: never more than the work units (whatever the
+        // split of the last wave makes of them: the peers count on this number) or one wave of SMs
         int n = a->fused_push->ctas_per_dest;
-        if (n > grid) n = int(grid);
+        if (n > units) n = int(units);
         if (n > sm_count()) n = sm_count();
         push.n_push_ctas = n;
     }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     return a->dtype == PA_BF16 ? launch_attn<true>(maps, p, push, int(grid), s, a->head_dim)
                                : launch_attn<false>(maps, p, push, int(grid), s, a->head_dim);
 }

@@ -17,6 +17,7 @@ import torch
 
 from . import _lib as L
 from . import _status
+from . import config
 
 __all__ = [
     "attention_forward_with_lse",
@@ -103,6 +104,22 @@ def pack_key_mask(key_mask: torch.Tensor, n_chunks: int, rows: int) -> torch.Ten
     return out
 
 
+_SPLIT_WS: dict = {}
+
+
+def split_workspace(device: torch.device, stream: int) -> torch.Tensor:
+    """Scratch memory for launches that split their last wave (pa_attn_args.workspace), one
+    buffer per device and stream: launches that may overlap must not share it."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    ws = _SPLIT_WS.get(key)
+    if ws is None:
+        if len(_SPLIT_WS) >= 16:  # (streams come and go)
+            _SPLIT_WS.clear()
+        ws = torch.empty(int(L.load().pa_attn_workspace_bytes()), dtype=torch.uint8, device=device)
+        _SPLIT_WS[key] = ws
+    return ws
+
+
 def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: bool,
                           status: Optional[torch.Tensor] = None, is_causal: bool = False,
                           key_mask: Optional[torch.Tensor] = None):
@@ -134,7 +151,11 @@ def raw_attention_forward(query, key, value, scale: Optional[float], need_lse: b
     a.wait_limit_ns = 0
     bits = pack_key_mask(key_mask, 1, Skv) if key_mask is not None else None
     a.key_bits = bits.data_ptr() if bits is not None else None
-    L.check(L.load().pa_attn_fwd(C.byref(a), torch.cuda.current_stream(query.device).cuda_stream))
+    stream = torch.cuda.current_stream(query.device).cuda_stream
+    if config.attention.split_last_wave and not is_causal:
+        ws = split_workspace(query.device, stream)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    L.check(L.load().pa_attn_fwd(C.byref(a), stream))
     if mirror is not None:
         mirror.refresh()
     return out, lse

@@ -66,6 +66,9 @@ class LocalCluster:
         self.capacity = None
         self.ws: List = []
         self.state = E.CallState()
+        # scratch for launches that split their last wave (None: no launch does); the emulated
+        # ranks' launches follow each other on one stream and may share it
+        self.split_ws = None
 
     def _ensure(self, plan0, B, sq, skv, D, esz):
         E = self.E
@@ -99,7 +102,8 @@ class LocalCluster:
         out = torch.empty((B, sq, H, D), dtype=q.dtype, device=self.device).transpose(1, 2)
         scale = (1.0 / math.sqrt(D)) if scale is None else scale
         E.launch_attention(plan, self.ws[0], par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par], wait_ns,
-                           torch.cuda.current_stream(self.device).cuda_stream, out, push, (q, k, v) if in_place else None)
+                           torch.cuda.current_stream(self.device).cuda_stream, out, push, (q, k, v) if in_place else None,
+                           split_ws=self.split_ws)
         torch.cuda.synchronize(self.device)
         code = int(self.ws[0].status_tensor().item())
         assert code == 0, f"device status {code}"
@@ -137,7 +141,8 @@ class LocalCluster:
             if self.U == 1:
                 outs[g] = torch.empty((B, sq, H, D), dtype=qs[g].dtype, device=self.device).transpose(1, 2)
             E.launch_attention(plans[g], self.ws[g], par, (B, H, sq, D), qs[g].dtype, skv, scale, st.arrive_expect[par],
-                               wait_ns, stream, outs[g], None, keep[g] if in_place else None, is_causal, key_bits)
+                               wait_ns, stream, outs[g], None, keep[g] if in_place else None, is_causal, key_bits,
+                               self.split_ws)
         if self.U > 1:
             st.done_expect[par] += E.out_tiles_per_call(plans[0], B, sq)
             for g in range(self.W):

@@ -41,12 +41,14 @@ def test_struct_layouts_match_c(tmp_path):
         '#include <stdio.h>\n#include <stddef.h>\n#include "pa_b200.h"\n'
         'int main(){printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(pa_attn_args), sizeof(pa_cp_attn_args),'
         ' sizeof(pa_push_job), sizeof(pa_cp_push_args), offsetof(pa_cp_attn_args, status),'
-        ' offsetof(pa_cp_push_args, flag), offsetof(pa_attn_args, status));}\n')
+        ' offsetof(pa_cp_push_args, flag), offsetof(pa_attn_args, status));'
+        'printf("%zu %zu\\n", offsetof(pa_attn_args, workspace), offsetof(pa_cp_attn_args, workspace_bytes));}\n')
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     want = [C.sizeof(L.AttnArgs), C.sizeof(L.CpAttnArgs), C.sizeof(L.PushJob), C.sizeof(L.CpPushArgs),
-            L.CpAttnArgs.status.offset, L.CpPushArgs.flag.offset, L.AttnArgs.status.offset]
+            L.CpAttnArgs.status.offset, L.CpPushArgs.flag.offset, L.AttnArgs.status.offset,
+            L.AttnArgs.workspace.offset, L.CpAttnArgs.workspace_bytes.offset]
     assert got == want
 
 
@@ -107,3 +109,31 @@ def test_new_entry_points_validate_without_a_device(lib):
     a.batch = a.heads = a.seq_q = a.seq_kv = 1
     a.head_dim, a.scale = 96, 1.0
     assert lib.pa_attn_fwd(C.byref(a), None) == L.PA_ENOTSUP and b"64 and 128" in lib.pa_last_error()
+
+
+def test_split_plan_of_the_last_wave(lib):
+    """Which launches give the units of their last wave to several CTAs (no device needed)."""
+    def plan(units, tiles, sms=148, d=128, causal=0, ws=None):
+        ws = lib.pa_attn_workspace_bytes() if ws is None else ws
+        f, k = C.c_int32(-1), C.c_int32(-1)
+        assert lib.pa_attn_split_plan(units, sms, tiles, d, causal, ws, C.byref(f), C.byref(k)) == 0
+        return f.value, k.value
+
+    assert lib.pa_attn_workspace_bytes() >= 440 * 256 * (8 + 128 * 4)
+    # 8 ranks of the headline workload: 384 units, 2.59 waves -> the last 88 units go to 5 CTAs each
+    assert plan(384, 256) == (296, 5)
+    # 4 ranks: 768 units, 28 in the last wave -> 140 CTAs, one round
+    assert plan(768, 256) == (740, 5)
+    # one GPU: 3072 units, 20.76 waves - nothing to gain
+    assert plan(3072, 256) == (3072, 1)
+    # whole waves, causal runs, no workspace, too few tiles per CTA: one launch
+    assert plan(296, 256) == (296, 1)
+    assert plan(384, 256, causal=1) == (384, 1)
+    assert plan(384, 256, ws=0) == (384, 1)
+    assert plan(384, 15) == (384, 1)
+    # a smaller workspace allows fewer CTAs per unit
+    f, k = plan(384, 256, ws=40 << 20)
+    assert f == 296 and 2 <= k < 5
+    # fewer units than SMs (FLUX-sized call on 8 ranks): 54 units -> 108 CTAs
+    assert plan(54, 36) == (0, 2)
+    assert lib.pa_attn_split_plan(0, 148, 1, 128, 0, 0, None, None) != 0

@@ -13,8 +13,16 @@ from helpers import (assert_attention_close, assert_lse_close, bf16_from_bits, o
 pytestmark = pytest.mark.gpu
 
 
-def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is_causal=False, key_bits=None):
-    from paraattention_b200 import _lib as L
+def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is_causal=False, key_bits=None,
+                   workspace="as the op"):
+    """pa_attn_fwd through ctypes. ``workspace``: a uint8 tensor, None (the launch never splits
+    its last wave), or by default what the custom op would pass."""
+    from paraattention_b200 import _lib as L, config, ops
+
+    if isinstance(workspace, str):
+        workspace = None
+        if config.attention.split_last_wave and not is_causal:
+            workspace = ops.split_workspace(q.device, torch.cuda.current_stream().cuda_stream)
 
     lib = L.load()
     B, H, Sq, D = q.shape
@@ -32,6 +40,8 @@ def _abi_attention(q, k, v, scale=None, want_lse=True, out=None, status=None, is
     for i in range(3):
         a.q_stride[i], a.k_stride[i], a.v_stride[i], a.o_stride[i] = q.stride(i), k.stride(i), v.stride(i), out.stride(i)
     a.status = status.data_ptr() if status is not None else None
+    if workspace is not None:
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     rc = lib.pa_attn_fwd(C.byref(a), torch.cuda.current_stream().cuda_stream)
     return rc, out, lse
 
@@ -356,3 +366,82 @@ def test_packed_key_mask_is_reused_until_the_mask_changes():
     m[0, 3] = ~m[0, 3]                                   # an in-place change bumps the version counter
     w2 = ops.pack_key_mask(m, 1, 200)
     assert w2 is not w1 and not torch.equal(w2, before)
+
+
+def _split_plan(units, kv_tiles, D, ws_bytes):
+    from paraattention_b200 import _lib as L
+
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    f, k = C.c_int32(), C.c_int32()
+    assert L.load().pa_attn_split_plan(units, sms, kv_tiles, D, 0, ws_bytes, C.byref(f), C.byref(k)) == 0
+    return f.value, k.value
+
+
+@pytest.mark.parametrize("B,H,Sq,Skv,D,dtype,masked", [
+    (1, 3, 8192, 8192, 128, torch.bfloat16, False),   # 96 units: fewer than SMs, one launch of shares
+    (1, 5, 8192, 4099, 128, torch.bfloat16, False),   # 160 units: a whole wave, then 12 split units; ragged keys
+    (2, 2, 4100, 6000, 64, torch.float16, False),     # head_dim 64, fp16, ragged query rows in the last pair
+    (1, 3, 4096, 5000, 128, torch.bfloat16, True),    # key mask words cross the shares
+])
+def test_abi_split_last_wave_matches_oracle(B, H, Sq, Skv, D, dtype, masked):
+    """With a workspace the units of an under-filled last wave are computed by several CTAs that
+    split the keys; the combined result must match the oracle like the one-CTA result does, and
+    the one-CTA result itself up to fp32 summation order."""
+    from paraattention_b200 import _lib as L
+
+    ws = torch.empty(int(L.load().pa_attn_workspace_bytes()), dtype=torch.uint8, device="cuda")
+    units = ((Sq + 255) // 256) * H * B
+    split_from, split_k = _split_plan(units, (Skv + 127) // 128, D, ws.numel())
+    assert split_k > 1 and split_from < units, "the shape is meant to exercise the split"
+    q, k, v = seeded_qkv(B, H, Sq, Skv, seed=Sq + 3 * Skv + D, dtype=dtype, D=D)
+    bits = mask = None
+    if masked:
+        g = torch.Generator(device="cpu").manual_seed(7)
+        mask = torch.rand(B, Skv, generator=g) > 0.3
+        mask[:, 1600:3500] = False  # every key of the middle share is masked: it weighs nothing
+        bits = _abi_pack(mask.cuda(), 1, Skv)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rc, out, lse = _abi_attention(q, k, v, status=status, key_bits=bits, workspace=ws)
+    assert rc == 0
+    rc, out1, lse1 = _abi_attention(q, k, v, status=status, key_bits=bits, workspace=None)
+    assert rc == 0
+    rc, out2, lse2 = _abi_attention(q, k, v, status=status, key_bits=bits, workspace=ws)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    # whichever CTA of a unit finishes last combines the shares, always in the same order
+    assert torch.equal(out2, out) and torch.equal(lse2, lse)
+    # the same numbers up to the order of fp32 additions and one rounding to 16 bits
+    assert (out.float() - out1.float()).abs().max().item() <= 2e-2 * out1.float().abs().max().item()
+    assert torch.allclose(out.float(), out1.float(), rtol=2e-2, atol=2e-3)
+    assert torch.allclose(lse, lse1, rtol=0, atol=2e-5)
+    # sampled rows against the oracle (the last rows of the last head sit in the split units)
+    gen = np.random.default_rng(5)
+    rows = np.unique(np.concatenate([gen.integers(0, Sq, 96), np.arange(Sq - 40, Sq)]))
+    for b, h in ((0, 0), (B - 1, H - 1)):
+        qn = q[b, h].float().cpu().numpy()[rows][None, None]
+        kn, vn = (t[b, h].float().cpu().numpy()[None, None] for t in (k, v))
+        if masked:
+            keep = mask[b].numpy()
+            kn, vn = kn[:, :, keep], vn[:, :, keep]
+        ref_out, ref_lse = O.sdpa_with_lse(qn, kn, vn)
+        assert_attention_close(out[b:b + 1, h:h + 1][:, :, rows], ref_out, f"split b{b} h{h}")
+        assert_lse_close(lse[b:b + 1, h:h + 1][:, :, rows], ref_lse)
+
+
+def test_split_last_wave_through_the_custom_op():
+    """The op passes a workspace by default; switching the split off gives the one-CTA result."""
+    from paraattention_b200 import config
+
+    q, k, v = seeded_qkv(1, 3, 8192, 8192, seed=11)
+    old = config.attention.split_last_wave
+    try:
+        config.attention.split_last_wave = True
+        out_s, lse_s = torch.ops.para_attn.attention_forward_with_lse(q, k, v)
+        config.attention.split_last_wave = False
+        out_1, lse_1 = torch.ops.para_attn.attention_forward_with_lse(q, k, v)
+    finally:
+        config.attention.split_last_wave = old
+    torch.cuda.synchronize()
+    assert torch.allclose(out_s.float(), out_1.float(), rtol=2e-2, atol=2e-3)
+    assert torch.allclose(lse_s, lse_1, rtol=0, atol=2e-5)

@@ -132,6 +132,59 @@ def test_world8_meshes_against_oracle(U, R, H, S):
             assert torch.equal(outs2[rank], outs[rank]), f"call {rep + 2} differs on rank {rank}"
 
 
+def _split_ws():
+    from paraattention_b200 import _lib as L
+
+    return torch.empty(int(L.load().pa_attn_workspace_bytes()), dtype=torch.uint8, device="cuda")
+
+
+@pytest.mark.parametrize("U,R,H,S,D,masked", [(2, 1, 4, 2 * 2048, 128, False), (1, 4, 2, 4 * 1100, 128, False),
+                                              (2, 2, 4, 4 * 1030, 64, False), (2, 2, 4, 4 * 1030, 128, True)])
+def test_split_last_wave_on_meshes_against_oracle(U, R, H, S, D, masked):
+    """Chunked launches whose units are shared by several CTAs (a workspace is given): the shares'
+    tile ranges cross the chunks of different source ranks, ragged chunk ends included."""
+    W = U * R
+    q, k, v = seeded_qkv(1, H, S, S, D=D, seed=U * 10 + R + 77)
+    mask = None
+    if masked:
+        g = torch.Generator().manual_seed(S)
+        mask = torch.rand(1, S, generator=g) < 0.7
+        mask[0, S // W: 2 * (S // W)] = False  # rank 1's keys are all padding
+    qs, ks, vs = ([t.contiguous() for t in x.chunk(W, dim=-2)] for x in (q, k, v))
+    cluster = LocalCluster(U, R)
+    plain = cluster.attention(qs, ks, vs, key_mask=None if mask is None else mask.cuda())
+    cluster.split_ws = _split_ws()
+    outs = cluster.attention(qs, ks, vs, key_mask=None if mask is None else mask.cuda())
+    again = cluster.attention(qs, ks, vs, key_mask=None if mask is None else mask.cuda())
+    whole, _ = O.sdpa_with_lse(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(),
+                               key_mask=None if mask is None else mask.numpy())
+    assert_attention_close(torch.cat(outs, dim=-2), whole, f"split {U}x{R}")
+    for rank in range(W):
+        assert torch.equal(again[rank], outs[rank]), "the order in which shares are combined is fixed"
+        assert torch.allclose(outs[rank].float(), plain[rank].float(), rtol=2e-2, atol=2e-3)
+    # the split did happen: a one-CTA result differs in the last bit somewhere
+    assert any(not torch.equal(outs[rank], plain[rank]) for rank in range(W))
+
+
+@pytest.mark.parametrize("B,H,S,ctas", [(1, 2, 4095, 8), (2, 3, 8192, 16)])
+def test_fused_push_with_split_last_wave(B, H, S, ctas):
+    """Pushers and a split last wave in one call: with fewer units than SMs the pushers lead the
+    launch of shares; with more they lead the launch of whole units and the shares follow."""
+    q, k, v = seeded_qkv(B, H, S, S, seed=S + 1, bshd=True)
+    cluster = LocalCluster(1, 1)
+    cluster.split_ws = _split_ws()
+    rows = np.unique(np.concatenate([np.arange(0, S, 97), np.arange(S - 64, S)]))
+    first = None
+    for rep in range(3):
+        out = cluster.attention_fused_single_rank(q, k, v, ctas=ctas)
+        first = out if first is None else first
+        assert torch.equal(out, first)
+    for b, h in ((0, 0), (B - 1, H - 1)):
+        ref, _ = O.sdpa_with_lse(q[b:b + 1, h:h + 1].float().cpu().numpy()[:, :, rows],
+                                 k[b:b + 1, h:h + 1].float().cpu().numpy(), v[b:b + 1, h:h + 1].float().cpu().numpy())
+        assert_attention_close(first[b:b + 1, h:h + 1][:, :, rows], ref, f"fused push + split b{b} h{h}")
+
+
 def test_sharded_equals_single_device_full_size_shard():
     """The reference's pinned contract (tests/test_interface.py:70): the sharded result is
     chunk r of single-device attention. Shard length 4095 = 32760 / 8 is not a tile multiple."""
