@@ -336,7 +336,7 @@ def run_ours(args):
         launches_per_step = 1 + (2 if U > 1 else 0) + (1 if causal else 0)
     # a launch whose last wave is split (the library decides per shape) is two launches
     split = split_plan(torch, dev, ((S_pad // world + 255) // 256) * (H // U) * U,
-                       ((S_pad // world + 127) // 128) * world, causal)
+                       ((S_pad // world + 127) // 128) * world, causal, world > 1)
     if split["k"] > 1 and split["from"] > 0:
         launches_per_step += 1
 
@@ -496,7 +496,7 @@ TRAFFIC_BYTES_PER_LAUNCH = {
 # ------------------------------------------------------------------------------------------
 # comparator: the reference's GPU path (library SDPA + NCCL) on the same GPUs
 # ------------------------------------------------------------------------------------------
-def split_plan(torch, dev, units, kv_tiles, causal):
+def split_plan(torch, dev, units, kv_tiles, causal, pushers):
     """What the attention launch of this shape does with its last wave: {"from", "k", "units"}
     (k = 1: one CTA per work unit everywhere)."""
     import ctypes as C
@@ -506,7 +506,8 @@ def split_plan(torch, dev, units, kv_tiles, causal):
     ws = int(lib.pa_attn_workspace_bytes()) if config.attention.split_last_wave else 0
     f, k = C.c_int32(units), C.c_int32(1)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    L.check(lib.pa_attn_split_plan(units, sms, kv_tiles, VARIANT["D"], int(causal), ws, C.byref(f), C.byref(k)))
+    L.check(lib.pa_attn_split_plan(units, sms, kv_tiles, VARIANT["D"], int(causal), int(pushers), ws, C.byref(f),
+                                   C.byref(k)))
     return {"units": units, "from": f.value, "k": k.value}
 
 

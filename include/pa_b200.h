@@ -93,11 +93,12 @@ int64_t pa_attn_workspace_bytes(void);
 
 /* What a launch with `units` work units (pairs of 128-row query tiles x heads x batch x query
  * chunks) and kv_tiles key/value tiles of 128 rows per unit does with a workspace of that size on
- * a device with sm_count SMs: units [0, *split_from) are computed by one CTA each, every later
+ * a device with sm_count SMs (fused_push != 0: a pa_cp_attn_fwd call whose leading CTAs push):
+ * units [0, *split_from) are computed by one CTA each, every later
  * unit by *split_k CTAs in a second launch (*split_k = 1, *split_from = units: one launch,
  * nothing split). Needs no device. */
 int pa_attn_split_plan(int64_t units, int32_t sm_count, int64_t kv_tiles, int32_t head_dim, int32_t is_causal,
-                       int64_t workspace_bytes, int32_t* split_from, int32_t* split_k);
+                       int32_t fused_push, int64_t workspace_bytes, int32_t* split_from, int32_t* split_k);
 
 int pa_attn_fwd(const pa_attn_args* args, void* stream);
 

@@ -122,7 +122,7 @@ def load() -> C.CDLL:
     lib.pa_attn_workspace_bytes.restype = C.c_int64
     lib.pa_attn_workspace_bytes.argtypes = []
     lib.pa_attn_split_plan.restype = C.c_int
-    lib.pa_attn_split_plan.argtypes = [C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int64,
+    lib.pa_attn_split_plan.argtypes = [C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int64,
                                        C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
     lib.pa_attn_fwd.restype = C.c_int
     lib.pa_attn_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]

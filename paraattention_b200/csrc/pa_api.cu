@@ -150,39 +150,48 @@ int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::Push
 // ceil(units / sms) rounds although the last round may be nearly empty (384 units on 148 SMs:
 // 2.59 rounds of work in the time of 3). With a workspace the units of the last round are each
 // given to k CTAs that take 1/k of the key/value tiles and combine their results in the
-// kernel's epilogue, so that the last round costs ceil(tail * k / sms) / k of a round instead
-// of a whole one. k is the value in [2, 8] with the lowest modelled cost (every extra CTA is
-// charged 2 % of a unit for its prologue and the exchange of partial results) that leaves at
-// least 8 tiles per CTA and fits the workspace; nothing is split unless the model promises 3 %
-// of the call. Causal runs (units of unequal length, long ones first) are left alone.
+// kernel's epilogue, so that the last round costs ceil(tail * k / sms) short rounds instead of a
+// whole one. Times are modelled from measurements on B200 (both head dims): 1.8 us per
+// key/value tile of a CTA plus 16 us per CTA for everything around the tile loop, 26 us for a
+// CTA that also exchanges partial results. k is the value in [2, 8] with the lowest modelled
+// time that leaves at least 8 tiles per CTA and fits the workspace; nothing is split unless the
+// model promises 3 % of the call. Causal runs (units of unequal length, long ones first) are
+// left alone, and so are launches whose first wave is led by pushing CTAs (`pushers`) unless a
+// unit has at least 128 tiles: the shares are a launch of their own that starts when the last
+// CTA of the whole waves has finished, and CTAs that push first finish tens of microseconds
+// after the others (measured on 2 GPUs at 36 tiles per unit: 257 us split, 218 us whole).
 struct TailSplit {
     int from = 0, k = 1;
     long long grid = 0;
     size_t cnt_bytes = 0, ml_bytes = 0, o_bytes = 0;
 };
 
-TailSplit plan_tail_split(long long units, int sms, long long kv_tiles, int head_dim, bool causal, int64_t ws_bytes) {
+TailSplit plan_tail_split(long long units, int sms, long long kv_tiles, int head_dim, bool causal, bool pushers,
+                          int64_t ws_bytes) {
     TailSplit r;
     r.from = int(units);
     r.grid = units;
     if (causal || ws_bytes <= 0 || sms <= 0 || units <= 0) return r;
     const long long tail = units % sms;
     if (tail == 0) return r;
-    const double rounds_now = double(units / sms + 1);
-    double best = 1.0;
+    if (pushers && units > sms && kv_tiles < 128) return r;
+    const double t_tile = 1.8, t_cta = 16.0, t_share = 26.0;  // microseconds
+    const double t_unit = double(kv_tiles) * t_tile + t_cta;
+    const double t_now = double(units / sms + 1) * t_unit;
+    double best = t_unit;
     int best_k = 1;
     for (int k = 2; k <= 8; ++k) {
         if (kv_tiles / k < 8) break;
         const size_t need = 256 + size_t(tail) * 9 * 4 + size_t(tail) * k * 256 * (8 + size_t(head_dim) * 4) + 512;
         if (need > size_t(ws_bytes)) break;
         const long long rounds = (tail * k + sms - 1) / sms;
-        const double cost = double(rounds) * (1.0 / k + 0.02);
-        if (cost < best - 1e-9) {
-            best = cost;
+        const double t = double(rounds) * (double((kv_tiles + k - 1) / k) * t_tile + t_share);
+        if (t < best - 1e-9) {
+            best = t;
             best_k = k;
         }
     }
-    if (best_k == 1 || (1.0 - best) / rounds_now < 0.03) return r;
+    if (best_k == 1 || (t_unit - best) / t_now < 0.03) return r;
     r.k = best_k;
     r.from = int(units - tail);
     r.grid = (units - tail) + tail * best_k;
@@ -193,14 +202,14 @@ TailSplit plan_tail_split(long long units, int sms, long long kv_tiles, int head
 }
 
 // Fills the split fields of `p` and zeroes the counters on the stream; returns the grid size.
-int apply_tail_split(pa::AttnParams* p, long long units, long long kv_tiles, int head_dim, void* ws, int64_t ws_bytes,
-                     cudaStream_t s, long long* grid) {
+int apply_tail_split(pa::AttnParams* p, long long units, long long kv_tiles, int head_dim, bool pushers, void* ws,
+                     int64_t ws_bytes, cudaStream_t s, long long* grid) {
     p->split_from = int(units);
     p->split_k = 1;
     *grid = units;
     if (ws == nullptr) return PA_OK;
     if ((reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return fail(PA_EINVAL, "workspace must be 256-byte aligned");
-    const TailSplit t = plan_tail_split(units, sm_count(), kv_tiles, head_dim, p->causal != 0, ws_bytes);
+    const TailSplit t = plan_tail_split(units, sm_count(), kv_tiles, head_dim, p->causal != 0, pushers, ws_bytes);
     if (t.k == 1) return PA_OK;
     if ((units - t.from) * t.k > 0x7fffffffLL) return PA_OK;
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -288,7 +297,8 @@ int attn_fwd_impl(const pa_attn_args* a, void* stream, long long* dbg_t = nullpt
     if (units > 0x7fffffffLL) return fail(PA_EINVAL, "problem too large for one launch");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     long long grid = units;
-    rc = apply_tail_split(&p, units, (a->seq_kv + 127) / 128, a->head_dim, a->workspace, a->workspace_bytes, s, &grid);
+    rc = apply_tail_split(&p, units, (a->seq_kv + 127) / 128, a->head_dim, false, a->workspace, a->workspace_bytes, s,
+                          &grid);
     if (rc != PA_OK) return rc;
     pa::PushParams push;
     memset(&push, 0, sizeof(push));
@@ -334,10 +344,11 @@ int pa_version(void) { return 1; }
 int64_t pa_attn_workspace_bytes(void) { return int64_t(64) << 20; }
 
 int pa_attn_split_plan(int64_t units, int32_t sm_count_, int64_t kv_tiles, int32_t head_dim, int32_t is_causal,
-                       int64_t workspace_bytes, int32_t* split_from, int32_t* split_k) {
+                       int32_t fused_push, int64_t workspace_bytes, int32_t* split_from, int32_t* split_k) {
     if (units <= 0 || sm_count_ <= 0 || kv_tiles <= 0 || (head_dim != 64 && head_dim != 128))
         return fail(PA_EINVAL, "units, sm_count and kv_tiles must be positive, head_dim 64 or 128");
-    const TailSplit t = plan_tail_split(units, sm_count_, kv_tiles, head_dim, is_causal != 0, workspace_bytes);
+    const TailSplit t = plan_tail_split(units, sm_count_, kv_tiles, head_dim, is_causal != 0, fused_push != 0,
+                                        workspace_bytes);
     if (split_from != nullptr) *split_from = t.from;
     if (split_k != nullptr) *split_k = t.k;
     return PA_OK;
@@ -458,7 +469,7 @@ int pa_cp_attn_fwd(const pa_cp_attn_args* a, void* stream) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     long long grid = units;
     rc = apply_tail_split(&p, units, static_cast<long long>((a->kv_rows + 127) / 128) * a->n_kv_chunks, a->head_dim,
-                          a->workspace, a->workspace_bytes, s, &grid);
+                          a->fused_push != nullptr, a->workspace, a->workspace_bytes, s, &grid);
     if (rc != PA_OK) return rc;
     pa::PushParams push;
     memset(&push, 0, sizeof(push));

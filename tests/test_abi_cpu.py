@@ -113,10 +113,10 @@ def test_new_entry_points_validate_without_a_device(lib):
 
 def test_split_plan_of_the_last_wave(lib):
     """Which launches give the units of their last wave to several CTAs (no device needed)."""
-    def plan(units, tiles, sms=148, d=128, causal=0, ws=None):
+    def plan(units, tiles, sms=148, d=128, causal=0, ws=None, push=0):
         ws = lib.pa_attn_workspace_bytes() if ws is None else ws
         f, k = C.c_int32(-1), C.c_int32(-1)
-        assert lib.pa_attn_split_plan(units, sms, tiles, d, causal, ws, C.byref(f), C.byref(k)) == 0
+        assert lib.pa_attn_split_plan(units, sms, tiles, d, causal, push, ws, C.byref(f), C.byref(k)) == 0
         return f.value, k.value
 
     assert lib.pa_attn_workspace_bytes() >= 440 * 256 * (8 + 128 * 4)
@@ -136,4 +136,7 @@ def test_split_plan_of_the_last_wave(lib):
     assert f == 296 and 2 <= k < 5
     # fewer units than SMs (FLUX-sized call on 8 ranks): 54 units -> 108 CTAs
     assert plan(54, 36) == (0, 2)
-    assert lib.pa_attn_split_plan(0, 148, 1, 128, 0, 0, None, None) != 0
+    # pushers lead the first wave: a second launch pays only when the units are long
+    assert plan(216, 36) == (148, 2) and plan(216, 36, push=1) == (216, 1)
+    assert plan(384, 256, push=1) == (296, 5) and plan(54, 36, push=1) == (0, 2)
+    assert lib.pa_attn_split_plan(0, 148, 1, 128, 0, 0, 0, None, None) != 0

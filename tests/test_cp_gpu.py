@@ -166,7 +166,7 @@ def test_split_last_wave_on_meshes_against_oracle(U, R, H, S, D, masked):
     assert any(not torch.equal(outs[rank], plain[rank]) for rank in range(W))
 
 
-@pytest.mark.parametrize("B,H,S,ctas", [(1, 2, 4095, 8), (2, 3, 8192, 16)])
+@pytest.mark.parametrize("B,H,S,ctas", [(1, 2, 4095, 8), (2, 3, 16384, 16)])
 def test_fused_push_with_split_last_wave(B, H, S, ctas):
     """Pushers and a split last wave in one call: with fewer units than SMs the pushers lead the
     launch of shares; with more they lead the launch of whole units and the shares follow."""
