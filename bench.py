@@ -334,7 +334,7 @@ def run_ours(args):
         # the attention kernel (the exchange rides inside it); Ulysses meshes add the one-warp
         # wait for the output tiles and the hand-out copy; causal runs one more one-warp wait
         launches_per_step = 1 + (2 if U > 1 else 0) + (1 if causal else 0)
-    # a launch whose last wave is split (the library decides per shape) is two launches
+    # a launch whose last wave is split (the library decides per shape; never with peers) is two launches
     split = split_plan(torch, dev, ((S_pad // world + 255) // 256) * (H // U) * U,
                        ((S_pad // world + 127) // 128) * world, causal, world > 1)
     if split["k"] > 1 and split["from"] > 0:

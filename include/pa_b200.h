@@ -171,7 +171,8 @@ typedef struct pa_cp_attn_args {
      * from pa_pack_key_mask. Lifts the reference's "no mask with ring attention" limit
      * (src/para_attn/para_attn_interface.py:228). */
     const uint64_t* key_bits;
-    /* Optional scratch, as in pa_attn_args (local device memory, never a peer's). */
+    /* Optional scratch, as in pa_attn_args (local device memory, never a peer's). Ignored when
+     * fused_push is given: behind pushing CTAs the split was measured slower. */
     void* workspace;
     int64_t workspace_bytes;
 } pa_cp_attn_args;

@@ -312,7 +312,9 @@ def build_attention_args(plan: CpPlan, ws: Workspace, par: int, shape, dtype: to
     if key_bits is not None:
         assert key_bits.shape == (B, plan.world, (skv + 63) // 64) and key_bits.is_contiguous()
         a.key_bits = key_bits.data_ptr()
-    if split_ws is not None:  # scratch for a split last wave (local memory of this engine)
+    # scratch for a split last wave: used by launches without pushers only (the engine's own
+    # launches push, and with real peers the split was measured slower: it passes none)
+    if split_ws is not None:
         a.workspace, a.workspace_bytes = split_ws.data_ptr(), split_ws.numel()
     return a
 
@@ -346,7 +348,6 @@ class CpEngine:
         self.capacity = (0, 0, 0)  # kv_chunk_bytes, q_chunk_bytes, out_bytes
         self.ws: Optional[Workspace] = None
         self.status: Optional[_status.StatusMirror] = None
-        self._split_buf: Optional[torch.Tensor] = None
         self.hdl = None
         self.state = CallState()
         self._launch_cache: Dict[Tuple, Tuple] = {}
@@ -359,16 +360,6 @@ class CpEngine:
             self.group_rank_of_plan[int(c[1]) * ulysses + int(c[0])] = i
         assert all(g >= 0 for g in self.group_rank_of_plan), "mesh coordinates are not unique"
         assert self.group_rank_of_plan[r * ulysses + u] == dist.get_rank(flat_group)
-
-    def _split_ws(self) -> Optional[torch.Tensor]:
-        """Scratch for launches that split their last wave; the engine's calls follow each other
-        on one stream, so one buffer serves them all."""
-        if not config.attention.split_last_wave:
-            return None
-        if self._split_buf is None:
-            self._split_buf = torch.empty(int(L.load().pa_attn_workspace_bytes()), dtype=torch.uint8,
-                                          device=self.device)
-        return self._split_buf
 
     def _ensure(self, need: Tuple[int, int, int]) -> None:
         if all(n <= c for n, c in zip(need, self.capacity)):
@@ -462,12 +453,12 @@ class CpEngine:
 
             key_bits = _ops.pack_key_mask(key_mask, self.world, skv)
         key = (B, H, sq, skv, D, q.dtype, par, n_push, scale, wait_ns, q.stride(), k.stride(), v.stride(),
-               is_causal, key_bits is not None, config.attention.split_last_wave)
+               is_causal, key_bits is not None)
         ent = self._launch_cache.get(key)
         if ent is None:
             push = build_push_args(plan, ws, par, q, k, v, n_push)
             a = build_attention_args(plan, ws, par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par],
-                                     wait_ns, out_local, push, (q, k, v), is_causal, key_bits, self._split_ws())
+                                     wait_ns, out_local, push, (q, k, v), is_causal, key_bits)
             which = [js.tensor for js in plan.push_jobs(skip_self=True)]
             ent = (a, push, which)
             if len(self._launch_cache) > 64:

@@ -24,9 +24,10 @@ class attention:
     # the shape-only transformers of this package prepare q, k, v with the fused kernel
     # (ops.qkv_prepare) instead of a chain of tensor operations when their tensors allow it
     fuse_qkv_prepare = os.getenv("PA_B200_FUSE_QKV_PREPARE", "1") == "1"
-    # non-causal attention launches whose last wave of CTAs would leave most SMs idle give the
-    # work units of that wave to several CTAs each (the keys are split among them; the library
-    # decides per shape). Costs one scratch buffer of 64 MB per device and stream.
+    # non-causal single-GPU attention launches whose last wave of CTAs would leave most SMs idle
+    # give the work units of that wave to several CTAs each (the keys are split among them; the
+    # library decides per shape). Costs one scratch buffer of 64 MB per device and stream.
+    # Context-parallel launches never do this (measured slower with real peers).
     split_last_wave = os.getenv("PA_B200_SPLIT_LAST_WAVE", "1") == "1"
 
 

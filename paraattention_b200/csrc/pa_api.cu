@@ -115,8 +115,7 @@ int launch_attn_inst(const CUtensorMap* maps, const pa::AttnParams& p, const pa:
 }
 
 // One launch over all work units, or - when the last wave is split - one over the whole waves
-// and a second one (no pushers: those belong to the first wave) in which every remaining unit
-// belongs to split_k CTAs.
+// and a second one in which every remaining unit belongs to split_k CTAs.
 template <bool kBF16>
 int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::PushParams& push, int grid,
                 cudaStream_t stream, int head_dim) {
@@ -128,10 +127,8 @@ int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::Push
             rc = launch_attn<kBF16>(maps, whole, push, p.split_from, stream, head_dim);
             if (rc != PA_OK) return rc;
         }
-        // (with fewer units than SMs there is no first launch, and the pushers lead this one)
-        pa::PushParams none;
-        memset(&none, 0, sizeof(none));
-        const pa::PushParams& tail_push = (p.split_from > 0) ? none : push;
+        pa::PushParams tail_push;  // (a launch with pushers is never split)
+        memset(&tail_push, 0, sizeof(tail_push));
         const int tail_grid = (grid - p.split_from) * p.split_k;
         pa::AttnParams tail = p;
         tail.unit_base = p.split_from;
@@ -156,10 +153,11 @@ int launch_attn(const CUtensorMap* maps, const pa::AttnParams& p, const pa::Push
 // CTA that also exchanges partial results. k is the value in [2, 8] with the lowest modelled
 // time that leaves at least 8 tiles per CTA and fits the workspace; nothing is split unless the
 // model promises 3 % of the call. Causal runs (units of unequal length, long ones first) are
-// left alone, and so are launches whose first wave is led by pushing CTAs (`pushers`) unless a
-// unit has at least 128 tiles: the shares are a launch of their own that starts when the last
-// CTA of the whole waves has finished, and CTAs that push first finish tens of microseconds
-// after the others (measured on 2 GPUs at 36 tiles per unit: 257 us split, 218 us whole).
+// left alone, and so are launches led by pushing CTAs (`pushers`): CTAs that push first, or
+// wait for a peer's chunk, finish tens of microseconds apart, and the launch of the shares
+// starts only when the last of them has finished. Measured with real peers, the split lost:
+// 8 GPUs at 256 tiles per unit 1.604 ms against 1.495 ms whole, at 36 tiles 260 us against
+// 222 us; 2 GPUs at 36 tiles 257 us against 218 us.
 struct TailSplit {
     int from = 0, k = 1;
     long long grid = 0;
@@ -174,7 +172,7 @@ TailSplit plan_tail_split(long long units, int sms, long long kv_tiles, int head
     if (causal || ws_bytes <= 0 || sms <= 0 || units <= 0) return r;
     const long long tail = units % sms;
     if (tail == 0) return r;
-    if (pushers && units > sms && kv_tiles < 128) return r;
+    if (pushers) return r;
     const double t_tile = 1.8, t_cta = 16.0, t_share = 26.0;  // microseconds
     const double t_unit = double(kv_tiles) * t_tile + t_cta;
     const double t_now = double(units / sms + 1) * t_unit;

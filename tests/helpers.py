@@ -102,8 +102,7 @@ class LocalCluster:
         out = torch.empty((B, sq, H, D), dtype=q.dtype, device=self.device).transpose(1, 2)
         scale = (1.0 / math.sqrt(D)) if scale is None else scale
         E.launch_attention(plan, self.ws[0], par, (B, H, sq, D), q.dtype, skv, scale, st.arrive_expect[par], wait_ns,
-                           torch.cuda.current_stream(self.device).cuda_stream, out, push, (q, k, v) if in_place else None,
-                           split_ws=self.split_ws)
+                           torch.cuda.current_stream(self.device).cuda_stream, out, push, (q, k, v) if in_place else None)
         torch.cuda.synchronize(self.device)
         code = int(self.ws[0].status_tensor().item())
         assert code == 0, f"device status {code}"

@@ -166,25 +166,6 @@ def test_split_last_wave_on_meshes_against_oracle(U, R, H, S, D, masked):
     assert any(not torch.equal(outs[rank], plain[rank]) for rank in range(W))
 
 
-@pytest.mark.parametrize("B,H,S,ctas", [(1, 2, 4095, 8), (2, 3, 16384, 16)])
-def test_fused_push_with_split_last_wave(B, H, S, ctas):
-    """Pushers and a split last wave in one call: with fewer units than SMs the pushers lead the
-    launch of shares; with more they lead the launch of whole units and the shares follow."""
-    q, k, v = seeded_qkv(B, H, S, S, seed=S + 1, bshd=True)
-    cluster = LocalCluster(1, 1)
-    cluster.split_ws = _split_ws()
-    rows = np.unique(np.concatenate([np.arange(0, S, 97), np.arange(S - 64, S)]))
-    first = None
-    for rep in range(3):
-        out = cluster.attention_fused_single_rank(q, k, v, ctas=ctas)
-        first = out if first is None else first
-        assert torch.equal(out, first)
-    for b, h in ((0, 0), (B - 1, H - 1)):
-        ref, _ = O.sdpa_with_lse(q[b:b + 1, h:h + 1].float().cpu().numpy()[:, :, rows],
-                                 k[b:b + 1, h:h + 1].float().cpu().numpy(), v[b:b + 1, h:h + 1].float().cpu().numpy())
-        assert_attention_close(first[b:b + 1, h:h + 1][:, :, rows], ref, f"fused push + split b{b} h{h}")
-
-
 def test_sharded_equals_single_device_full_size_shard():
     """The reference's pinned contract (tests/test_interface.py:70): the sharded result is
     chunk r of single-device attention. Shard length 4095 = 32760 / 8 is not a tile multiple."""
