@@ -67,6 +67,57 @@ def sdpa_with_lse(q: Array, k: Array, v: Array, *, scale: Optional[float] = None
     return out, lse
 
 
+def split_key_shares(n_tiles: int, k: int) -> List[Tuple[int, int]]:
+    """Tile ranges [begin, end) of the k CTAs that share one work unit of a split last wave:
+    share i takes tiles [n*i/k, n*(i+1)/k) of the unit's tile list (integer division). No
+    counterpart in the reference, whose library kernels schedule themselves."""
+    return [(n_tiles * i // k, n_tiles * (i + 1) // k) for i in range(k)]
+
+
+def combine_key_shares(q: Array, k: Array, v: Array, shares: Sequence[Tuple[int, int]], *, tile: int = 128,
+                       scale: Optional[float] = None, key_mask: Optional[Array] = None,
+                       stale: Optional[Sequence[float]] = None) -> Tuple[Array, Array]:
+    """Attention computed share by share over ranges of key tiles and combined the way the
+    split epilogue does: every share yields an unnormalised output O_i, a reference m_i and a
+    row sum l_i (both relative to m_i); the result is
+    sum_i e^(m_i - m) O_i / sum_i e^(m_i - m) l_i with m = max_i m_i, shares added in index order,
+    a share without any visible key (m_i = -inf) weighing nothing. ``stale[i]`` subtracts a
+    constant from share i's true row maximum to stand for the kernel's lazily updated reference:
+    the result must not depend on it."""
+    q = np.asarray(q, dtype=np.float32)
+    k = np.asarray(k, dtype=np.float32)
+    v = np.asarray(v, dtype=np.float32)
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    parts = []
+    for i, (t0, t1) in enumerate(shares):
+        sl = slice(t0 * tile, min(t1 * tile, k.shape[-2]))
+        s = np.matmul(q, np.swapaxes(k[..., sl, :], -1, -2)) * np.float32(scale)
+        if key_mask is not None:
+            s = np.where(np.asarray(key_mask, dtype=bool)[:, None, None, sl], s, np.float32(-np.inf))
+        m = s.max(axis=-1, keepdims=True) if s.shape[-1] else np.full(s.shape[:-1] + (1,), -np.inf, np.float32)
+        if stale is not None:
+            m = m - np.float32(stale[i])
+        with np.errstate(invalid="ignore"):
+            p = np.where(np.isneginf(m), np.float32(0), np.exp(s - np.where(np.isneginf(m), np.float32(0), m)))
+        parts.append((m, p.sum(axis=-1, keepdims=True), np.matmul(p, v[..., sl, :])))
+    m_tot = parts[0][0]
+    for m, _, _ in parts[1:]:
+        m_tot = np.maximum(m_tot, m)
+    acc_o = np.zeros_like(parts[0][2])
+    acc_l = np.zeros_like(parts[0][1])
+    for m, l, o in parts:
+        with np.errstate(invalid="ignore"):
+            w = np.where(np.isneginf(m), np.float32(0), np.exp(m - np.where(np.isneginf(m_tot), np.float32(0), m_tot)))
+        acc_o += o * w
+        acc_l += l * w
+    dead = ~(acc_l > 0)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        out = np.where(dead, np.float32(0), acc_o / np.where(dead, np.float32(1), acc_l))
+        lse = np.where(dead, np.float32(-np.inf), m_tot + np.log(np.where(dead, np.float32(1), acc_l)))[..., 0]
+    return out, lse
+
+
 def _sigmoid(x: Array) -> Array:
     return 1.0 / (1.0 + np.exp(-x))
 

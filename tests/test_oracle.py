@@ -180,3 +180,33 @@ def test_key_mask_composes_with_chunks():
         out, lse = np.where(dead[..., None], out, m_out), np.where(dead, lse, m_lse)
     np.testing.assert_allclose(out, whole, rtol=2e-5, atol=2e-6)
     np.testing.assert_allclose(lse, whole_lse, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("k", [2, 3, 5])
+def test_shares_of_a_split_unit_combine_to_whole_attention(k):
+    """What the split of an under-filled last wave relies on: attention over disjoint ranges of
+    key tiles, each with its own (possibly stale) reference, combines exactly to attention over
+    all keys - also when one share sees no key at all, and with a ragged last tile."""
+    rng = np.random.default_rng(k)
+    n_keys, tile = 8 * 16 + 5, 8           # 17 tiles, the last one ragged
+    q = rng.standard_normal((2, 2, 24, 16)).astype(np.float32)
+    kk, v = (rng.standard_normal((2, 2, n_keys, 16)).astype(np.float32) for _ in range(2))
+    shares = O.split_key_shares((n_keys + tile - 1) // tile, k)
+    assert shares[0][0] == 0 and shares[-1][1] == 17 and all(a[1] == b[0] for a, b in zip(shares, shares[1:]))
+    whole, whole_lse = O.sdpa_with_lse(q, kk, v)
+    out, lse = O.combine_key_shares(q, kk, v, shares, tile=tile)
+    np.testing.assert_allclose(out, whole, rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(lse, whole_lse, rtol=2e-5, atol=2e-6)
+    # references that lag behind the true maximum by up to 2^8 (as the kernel's may) change nothing
+    out_s, lse_s = O.combine_key_shares(q, kk, v, shares, tile=tile, stale=[0.7 * i for i in range(k)])
+    np.testing.assert_allclose(out_s, whole, rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(lse_s, whole_lse, rtol=2e-5, atol=2e-6)
+    # every key of the second share masked, and batch element 1 without any key at all
+    mask = rng.random((2, n_keys)) < 0.7
+    mask[0, shares[1][0] * tile:shares[1][1] * tile] = False
+    mask[1] = False
+    whole, whole_lse = O.sdpa_with_lse(q, kk, v, key_mask=mask)
+    out, lse = O.combine_key_shares(q, kk, v, shares, tile=tile, key_mask=mask)
+    np.testing.assert_allclose(out, whole, rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(lse[0], whole_lse[0], rtol=2e-5, atol=2e-6)
+    assert np.isneginf(lse[1]).all() and not out[1].any()
