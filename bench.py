@@ -147,6 +147,19 @@ def cpu_sample(H, S, budget_s=12.0, ref_dir=None):
             f"{torch.get_num_threads()} threads, {spent:.1f} s", kind)
 
 
+def bench_config(H, S, U, R):
+    """The `config` object of a bench line: the same for every arm run with the same flags."""
+    return {"workload": workload_name(H, S), "mesh": f"{U}x{R} (ulysses x ring)",
+            "l2": "256 MB flush between timed iterations", "timing": "CUDA events per step, max over ranks"}
+
+
+def mesh_of(args, world):
+    if args.mesh:
+        U, R = (int(x) for x in args.mesh.lower().split("x"))
+        return U, R
+    return world, 1
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -167,7 +180,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": wall / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(H, S), "note": "the reference's CPU path at world size 1, host cores"},
+        "config": bench_config(H, S, *mesh_of(args, max(args.gpus, 1))),
+        "note": "the reference's CPU path at world size 1 on the host cores (no GPU work: l2 and timing describe the GPU arm)",
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -465,9 +479,7 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": workload_name(H, S), "mesh": f"{U}x{R} (ulysses x ring)", "per_gpu_tflops": per_gpu_tflops,
-                   "l2": "256 MB flush between timed iterations", "timing": "CUDA events per step, max over ranks",
-                   "split_last_wave": split},
+        "config": bench_config(H, S, U, R), "per_gpu_tflops": per_gpu_tflops, "split_last_wave": split,
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "parity": parity,
         "gpu_launches": launches_per_step * args.steps,
     }
@@ -641,9 +653,7 @@ def run_reference_gpu(args, c):
             line = {"impl": "reference_gpu", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
                     "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": flops / value / 1e9,
                     "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                    "config": {"workload": workload_name(H, c["S_pad"]), "mesh": f"{U}x{R} (ulysses x ring)",
-                               "per_gpu_tflops": value / world, "l2": "256 MB flush between timed iterations",
-                               "timing": "CUDA events per step, max over ranks"},
+                    "config": bench_config(H, c["S_pad"], U, R), "per_gpu_tflops": value / world,
                     "backends_tflops": backends, "backend_errors": errors, "best_backend": best,
                     "kind": "reference package" if ref_pkg is not None else
                             "the reference's sequence of library calls (torch SDPA, NCCL all_to_all, torch ring loop) issued from bench.py",
